@@ -377,7 +377,7 @@ def min_gru(zxg, b_z, b_x, state, step, write_state=True):
 
 
 def gated_delta(qkv, b, a, gate, a_log, dt_bias, norm_w, eps, state, step, heads, kv_heads, dim, vdim, write_state=True,
-                unit_eps=1e-6):
+                unit_eps=1e-6, channel_decay=False, gate_act="silu"):
     N = qkv.shape[0]
     H, G, D, V = heads, kv_heads, dim, vdim
     x = _f(qkv)
@@ -387,7 +387,10 @@ def gated_delta(qkv, b, a, gate, a_log, dt_bias, norm_w, eps, state, step, heads
     q = q * torch.rsqrt((q * q).sum(-1, keepdim=True) + unit_eps) * D ** -0.5
     k = k * torch.rsqrt((k * k).sum(-1, keepdim=True) + unit_eps)
     beta = torch.sigmoid(_f(b))
-    g = torch.exp(-torch.exp(a_log) * _softplus(_f(a) + dt_bias))
+    if channel_decay:                                            # one decay per head and key channel: [N, H, D]
+        g = torch.exp(-torch.exp(a_log)[None, :, None] * _softplus(_f(a) + dt_bias).reshape(N, H, D))
+    else:
+        g = torch.exp(-torch.exp(a_log) * _softplus(_f(a) + dt_bias))[:, :, None].expand(N, H, D)
     rep = H // G
     o = torch.zeros((N, H, V), dtype=torch.float32, device=qkv.device)
     for lo, hi, slot in _spans(step, state):
@@ -395,14 +398,15 @@ def gated_delta(qkv, b, a, gate, a_log, dt_bias, norm_w, eps, state, step, heads
         for t in range(lo, hi):
             kt = k[t].repeat_interleave(rep, dim=0)              # [H, D]
             qt = q[t].repeat_interleave(rep, dim=0)
-            S = g[t][:, None, None] * S
+            S = g[t][:, :, None] * S
             u = beta[t][:, None] * (v[t] - torch.einsum("hdv,hd->hv", S, kt))
             S = S + kt[:, :, None] * u[:, None, :]
             o[t] = torch.einsum("hdv,hd->hv", S, qt)
         if write_state:
             state[slot] = S
     o = o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps) * norm_w
-    return (o * _silu(_f(gate)).reshape(N, H, V)).reshape(N, H * V).to(qkv.dtype)
+    act = torch.sigmoid(_f(gate)) if gate_act == "sigmoid" else _silu(_f(gate))
+    return (o * act.reshape(N, H, V)).reshape(N, H * V).to(qkv.dtype)
 
 
 def value_norm_pad(qkv, heads, kv_heads, dim, vdim, eps, normed=True):
@@ -502,9 +506,10 @@ def latent_prepare(q, dkv, norm_w, eps, table, step, cache, heads, dim, rot_dim,
     return q_rot
 
 
-def latent_attention(q_lat, q_rot, step, cache, heads, rank, rot_dim, scale):
+def latent_attention(q_lat, q_rot, step, cache, heads, rank, rot_dim, scale, impl=None, sink=None):
     """Causal attention of every head against the cached rows [latent | rotated key part]: scores
-    (q_lat . latent + q_rot . key part) * scale, output sum_j p_j latent_j, [N, H, rank]."""
+    (q_lat . latent + q_rot . key part) * scale, output sum_j p_j latent_j, [N, H, rank].  `sink` [H]: one more
+    term exp(sink_h) in the denominator."""
     N = q_lat.shape[0]
     ps = cache.page_size
     out = torch.empty((N, heads, rank), dtype=q_lat.dtype, device=q_lat.device)
@@ -523,7 +528,12 @@ def latent_attention(q_lat, q_rot, step, cache, heads, rank, rot_dim, scale):
         qpos = torch.arange(ctx[s], total, device=q_lat.device)[:, None]
         kpos = torch.arange(total, device=q_lat.device)[None, :]
         sc = sc.masked_fill((kpos > qpos)[None], float("-inf"))
-        out[a:b] = torch.einsum("hnk,kr->nhr", torch.softmax(sc, dim=-1), rows[:, :rank]).to(q_lat.dtype)
+        if sink is not None:
+            extra = _f(sink)[:, None, None].expand(heads, b - a, 1)
+            prob = torch.softmax(torch.cat([sc, extra], dim=-1), dim=-1)[..., :total]
+        else:
+            prob = torch.softmax(sc, dim=-1)
+        out[a:b] = torch.einsum("hnk,kr->nhr", prob, rows[:, :rank]).to(q_lat.dtype)
     return out
 
 
@@ -540,3 +550,31 @@ def linear_clamped_glu(x, w_gate_up, ff_dim, limit, alpha):
 def scale_softcap(logits, scale, cap):
     y = _f(logits) * scale
     return y if cap is None else cap * torch.tanh(y / cap)
+
+
+def rmsnorm_rows(x, w, eps):
+    """RMS norm of activation rows with a 32-bit weight (or None), computed in 32-bit, in x's dtype."""
+    v = _f(x)
+    y = v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps)
+    return (y if w is None else y * w).to(x.dtype)
+
+
+def routed_experts(x, w_router, w_gate_up, w_down, top, renorm=False, weight_on="input"):
+    """Every row to the `top` experts with the largest sigmoid(x . w_router^T); the scores weigh the experts' inputs
+    or outputs; w_gate_up [E, 2F, W] (gate rows, then up rows), w_down [E, W, F]."""
+    N, W = x.shape
+    E, F = w_gate_up.shape[0], w_gate_up.shape[1] // 2
+    s = torch.sigmoid(_f(x) @ _f(w_router).t())
+    val, idx = torch.topk(s, int(top), dim=-1)
+    if renorm:
+        val = val / val.sum(-1, keepdim=True)
+    out = torch.zeros((N, W), dtype=torch.float32, device=x.device)
+    for n in range(N):
+        for k in range(int(top)):
+            e, w = int(idx[n, k]), val[n, k]
+            xin = (_f(x[n]) * w).to(x.dtype) if weight_on == "input" else x[n]
+            gu = _f(xin) @ _f(w_gate_up[e]).t()
+            act = (_silu(gu[:F]) * gu[F:]).to(x.dtype)
+            y = _f(act) @ _f(w_down[e]).t()
+            out[n] += y if weight_on == "input" else y * w
+    return out.to(x.dtype)

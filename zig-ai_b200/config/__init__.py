@@ -3,3 +3,4 @@ from .base import (ConfigError, ModelConfig, config_from_dict, known_architectur
 from .lfm2 import Lfm2Config, adjusted_ff_dim
 from .pikasun import PikasunConfig
 from .vunolorn import VunolornConfig
+from .zikevik import ZikevikConfig

@@ -60,6 +60,10 @@ class ModelConfig:
     def field_dict(self) -> Dict[str, Any]:
         return {f.name: getattr(self, f.name) for f in fields(self)}
 
+    def complete(self, shapes: Dict[str, Tuple[int, ...]]) -> None:
+        """Fill in sizes that the architecture's config.json leaves to the stored tensors' shapes (`shapes`: stored name
+        -> shape).  Called by `load_config` for a model folder that holds tensors; most architectures need nothing."""
+
 
 # architecture name -> (config class, function(config) -> ModelSpec)
 _ARCHITECTURES: Dict[str, Tuple[type, Callable]] = {}
@@ -116,7 +120,22 @@ def load_config(model_dir_or_file: str) -> ModelConfig:
             d = json.load(f)
     except json.JSONDecodeError as e:
         raise ConfigError(f"{path}: not valid JSON ({e})") from e
-    return config_from_dict(d, where=path)
+    cfg = config_from_dict(d, where=path)
+    if type(cfg).complete is not ModelConfig.complete:
+        cfg.complete(_stored_shapes(os.path.dirname(path)))
+    return cfg
+
+
+def _stored_shapes(model_dir: str) -> Dict[str, Tuple[int, ...]]:
+    """Name -> shape of every tensor stored in the folder's .safetensors files (headers only; {} if there are none)."""
+    import glob
+    from ..weights.safetensors_io import SafetensorsFile
+    shapes = {}
+    for p in sorted(glob.glob(os.path.join(model_dir, "*.safetensors"))):
+        f = SafetensorsFile(p)
+        for name in f.names():
+            shapes.setdefault(name, tuple(f.info(name)[1]))
+    return shapes
 
 
 def save_config(cfg: ModelConfig, model_dir: str) -> str:

@@ -5,6 +5,9 @@
 //   s_j = (q_lat . c_j + q_rot . r_j) * scale                  for cached positions j <= pos, same request
 //   o   = sum_j softmax(s)_j c_j                               [R] per row and head
 //
+// With `sink` (one 32-bit number per head) the softmax's denominator holds one more term, exp(sink_h): it has no
+// key and no value, is not scaled, and counts once for a row whatever the number of key ranges.
+//
 // A block owns one row of the step and up to LA_WARPS heads (one warp a head).  The cached rows are brought into
 // shared memory 32 at a time, once for all heads of the block, as 32-bit values; lane j of every warp scores key j
 // (rows are padded by one word, so the lanes read different banks), the warp keeps an online softmax, and every lane
@@ -19,7 +22,7 @@ template <typename T, int MAXR>
 __global__ void __launch_bounds__(LA_WARPS * 32) latent_attention_kernel(
     T* __restrict__ out, const T* __restrict__ q_lat, const T* __restrict__ q_rot, const T* __restrict__ pages,
     const int* __restrict__ block_table, int table_width, const int* __restrict__ positions, const int* __restrict__ seq_idx,
-    int page_size, int H, int R, int Dr, float scale, int num_pages, int* __restrict__ status) {
+    int page_size, int H, int R, int Dr, float scale, int num_pages, int* __restrict__ status, const float* __restrict__ sink) {
     extern __shared__ float smem[];
     const int W = R + Dr, WP = W + 1;
     float* qs = smem;                                   // [LA_WARPS][W]  the block's queries, scaled
@@ -86,6 +89,12 @@ __global__ void __launch_bounds__(LA_WARPS * 32) latent_attention_kernel(
         m = m_new;
     }
     if (!live) return;
+    if (sink) {                                          // one more term of the denominator
+        const float sk = sink[h], m_new = fmaxf(m, sk), corr = expf(m - m_new);
+        l = l * corr + expf(sk - m_new);
+#pragma unroll
+        for (int r = 0; r < MAXR; ++r) acc[r] *= corr;
+    }
     const float inv = 1.f / l;
     T* orow = out + ((size_t)t * H + h) * R;
 #pragma unroll
@@ -98,7 +107,7 @@ __global__ void __launch_bounds__(LA_WARPS * 32) latent_attention_kernel(
 template <typename T, int MAXR>
 static int launch_latent(void* out, const void* q_lat, const void* q_rot, const void* pages, const int* block_table, int table_width,
                          const int* positions, const int* seq_idx, int page_size, int N, int H, int R, int Dr, float scale,
-                         int num_pages, int* status, cudaStream_t stream) {
+                         int num_pages, int* status, const float* sink, cudaStream_t stream) {
     const int W = R + Dr;
     const size_t smem = ((size_t)LA_WARPS * W + (size_t)LA_KEYS * (W + 1)) * sizeof(float);
     static unsigned long long done = 0;
@@ -106,7 +115,7 @@ static int launch_latent(void* out, const void* q_lat, const void* q_rot, const 
         cudaFuncSetAttribute(latent_attention_kernel<T, MAXR>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     return launch_pdl(latent_attention_kernel<T, MAXR>, dim3(N, (H + LA_WARPS - 1) / LA_WARPS), dim3(LA_WARPS * 32), smem, stream,
                       (T*)out, (const T*)q_lat, (const T*)q_rot, (const T*)pages, block_table, table_width, positions, seq_idx,
-                      page_size, H, R, Dr, scale, num_pages, status);
+                      page_size, H, R, Dr, scale, num_pages, status, sink);
 }
 
 // ------------------------------------------------------------------------------------------ tensor cores (bfloat16)
@@ -219,12 +228,24 @@ __device__ __forceinline__ void lm_tile(float (&o)[LM_COLS / 8][4], float& m0, f
     }
 }
 
+// The factors that turn a row's unnormalised sums into its output when the denominator also holds 2^(sink log2 e): with
+// M the row's maximum (base 2, scaled) and Mn = max(M, sink'), out = O 2^(M - Mn) / (l 2^(M - Mn) + 2^(sink' - Mn)).
+__device__ __forceinline__ void lm_sink(float& inv0, float& inv1, float l0, float l1, float M0, float M1,
+                                        const float* __restrict__ sink, int ha, int hb, int H) {
+    const float s0 = (ha < H ? sink[ha] : 0.f) * 1.4426950408889634f, s1 = (hb < H ? sink[hb] : 0.f) * 1.4426950408889634f;
+    const float n0 = fmaxf(M0, s0), n1 = fmaxf(M1, s1);
+    const float c0 = fast_exp2(M0 - n0), c1 = fast_exp2(M1 - n1);
+    inv0 = c0 / (l0 * c0 + fast_exp2(s0 - n0));
+    inv1 = c1 / (l1 * c1 + fast_exp2(s1 - n1));
+}
+
 template <int LM_COLS>       // output columns per warp: 128 or 256
 __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, const bf16* __restrict__ q_lat,
     const bf16* __restrict__ q_rot, const bf16* __restrict__ pages, const int* __restrict__ block_table, int table_width,
     const int* __restrict__ positions, const int* __restrict__ seq_idx, int page_size, int N, int H, int R, int Dr,
-    float scale_log2, int split_keys, int n_splits, int warps_per_block, int num_pages, int* __restrict__ status) {
+    float scale_log2, int split_keys, int n_splits, int warps_per_block, int num_pages, int* __restrict__ status,
+    const float* __restrict__ sink) {
     extern __shared__ __align__(16) unsigned char lm_smem[];
     const int W = R + Dr, ST = W + 8;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -295,7 +316,8 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     const int ha = h0 + g, hb = ha + 8;
     if (n_splits == 1) {
-        const float inv0 = 1.f / l0, inv1 = 1.f / l1;
+        float inv0 = 1.f / l0, inv1 = 1.f / l1;
+        if (sink) lm_sink(inv0, inv1, l0, l1, m0 * scale_log2, m1 * scale_log2, sink, ha, hb, H);
 #pragma unroll
         for (int j = 0; j < LM_COLS / 8; ++j) {
             const int d = j * 8 + 2 * tq;
@@ -338,7 +360,7 @@ __global__ void __launch_bounds__(128) latent_attention_rows_kernel(
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, const bf16* __restrict__ q_lat,
     const bf16* __restrict__ q_rot, const bf16* __restrict__ pages, const int* __restrict__ block_table, int table_width,
     const int* __restrict__ positions, const int* __restrict__ seq_idx, int page_size, int N, int H, int R, int Dr,
-    float scale_log2, int split_keys, int n_splits, int num_pages, int* __restrict__ status) {
+    float scale_log2, int split_keys, int n_splits, int num_pages, int* __restrict__ status, const float* __restrict__ sink) {
     extern __shared__ __align__(16) unsigned char lm_smem[];
     __shared__ int s_key[4], s_khi[4];
     const int W = R + Dr, ST = W + 8;
@@ -440,7 +462,8 @@ __global__ void __launch_bounds__(128) latent_attention_rows_kernel(
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     if (n_splits == 1) {
-        const float inv0 = 1.f / l0, inv1 = 1.f / l1;
+        float inv0 = 1.f / l0, inv1 = 1.f / l1;
+        if (sink) lm_sink(inv0, inv1, l0, l1, m0 * scale_log2, m1 * scale_log2, sink, ha, hb, H);
 #pragma unroll
         for (int j = 0; j < LM_COLS / 8; ++j) {
             const int d = j * 8 + 2 * tq;
@@ -475,14 +498,15 @@ __global__ void __launch_bounds__(128) latent_attention_rows_kernel(
 
 // out[t, h, :] = sum_c O_c 2^(m_c - m) / sum_c l_c 2^(m_c - m), the ranges taken in order
 __global__ void latent_combine_kernel(bf16* __restrict__ out, const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                      int R, int n_splits) {
+                                      int R, int n_splits, int H, const float* __restrict__ sink) {
     pdl_trigger();
     pdl_wait();
     const size_t th = blockIdx.x;
     const float* ml = part_ml + th * n_splits * 2;
-    float m = -INFINITY;
+    const float sk = sink ? sink[th % H] * 1.4426950408889634f : -INFINITY;
+    float m = sk;
     for (int c = 0; c < n_splits; ++c) m = fmaxf(m, ml[2 * c]);
-    float l = 0.f;
+    float l = sink ? fast_exp2(sk - m) : 0.f;
     for (int c = 0; c < n_splits; ++c) l += ml[2 * c + 1] * fast_exp2(ml[2 * c] - m);
     const float inv = 1.f / l;
     for (int d = threadIdx.x; d < R; d += blockDim.x) {
@@ -504,7 +528,7 @@ ZAI_API int zai_latent_attention_mma_supports(int R, int Dr) {
 ZAI_API int zai_latent_attention_mma(void* out, float* part_o, float* part_ml, const void* q_lat, const void* q_rot, const void* pages,
                                      const int* block_table, int table_width, const int* positions, const int* seq_idx,
                                      int page_size, int N, int H, int R, int Dr, float scale, int split_keys, int n_splits,
-                                     int num_pages, int* status, cudaStream_t stream) {
+                                     int num_pages, int* status, const float* sink, cudaStream_t stream) {
     if (N <= 0) return ZAI_OK;
     if (!zai_latent_attention_mma_supports(R, Dr) || H < 1 || n_splits < 1 || split_keys < LM_KT || split_keys % LM_KT) return ZAI_BAD_SIZE;
     const int cols = R <= 128 ? 128 : 256;
@@ -524,10 +548,10 @@ ZAI_API int zai_latent_attention_mma(void* out, float* part_o, float* part_ml, c
         auto rows_kernel = cols == 128 ? latent_attention_rows_kernel<128> : latent_attention_rows_kernel<256>;
         int rc = launch_pdl(rows_kernel, dim3((unsigned)blocks), dim3(128), smem, stream, (bf16*)out, part_o, part_ml,
                             (const bf16*)q_lat, (const bf16*)q_rot, (const bf16*)pages, block_table, table_width, positions, seq_idx,
-                            page_size, N, H, R, Dr, scale * 1.4426950408889634f, split_keys, n_splits, num_pages, status);
+                            page_size, N, H, R, Dr, scale * 1.4426950408889634f, split_keys, n_splits, num_pages, status, sink);
         if (rc != 0 || n_splits == 1) return rc;
         return launch_pdl(latent_combine_kernel, dim3((unsigned)((size_t)N * H)), dim3(128), 0, stream, (bf16*)out,
-                          (const float*)part_o, (const float*)part_ml, R, n_splits);
+                          (const float*)part_o, (const float*)part_ml, R, n_splits, H, sink);
     }
     const size_t per_warp = (size_t)(16 + 2 * LM_KT) * (R + Dr + 8) * 2;
     int wpb = (int)((200 * 1024) / per_warp);
@@ -543,22 +567,22 @@ ZAI_API int zai_latent_attention_mma(void* out, float* part_o, float* part_ml, c
     auto kernel = cols == 128 ? latent_attention_mma_kernel<128> : latent_attention_mma_kernel<256>;
     int rc = launch_pdl(kernel, dim3((unsigned)blocks), dim3(128), per_warp * wpb, stream, (bf16*)out, part_o,
                         part_ml, (const bf16*)q_lat, (const bf16*)q_rot, (const bf16*)pages, block_table, table_width, positions,
-                        seq_idx, page_size, N, H, R, Dr, scale * 1.4426950408889634f, split_keys, n_splits, wpb, num_pages, status);
+                        seq_idx, page_size, N, H, R, Dr, scale * 1.4426950408889634f, split_keys, n_splits, wpb, num_pages, status, sink);
     if (rc != 0 || n_splits == 1) return rc;
     return launch_pdl(latent_combine_kernel, dim3((unsigned)((size_t)N * H)), dim3(128), 0, stream, (bf16*)out, (const float*)part_o,
-                      (const float*)part_ml, R, n_splits);
+                      (const float*)part_ml, R, n_splits, H, sink);
 }
 
-// out [N, H, R], q_lat [N, H, R], q_rot [N, H, Dr], pages [num_pages, page_size, R + Dr], all in `dtype`.
+// out [N, H, R], q_lat [N, H, R], q_rot [N, H, Dr], pages [num_pages, page_size, R + Dr], all in `dtype`; sink [H] 32-bit or null.
 ZAI_API int zai_latent_attention(void* out, const void* q_lat, const void* q_rot, const void* pages, int dtype, const int* block_table,
                                  int table_width, const int* positions, const int* seq_idx, int page_size, int N, int H, int R,
-                                 int Dr, float scale, int num_pages, int* status, cudaStream_t stream) {
+                                 int Dr, float scale, int num_pages, int* status, const float* sink, cudaStream_t stream) {
     if (N <= 0) return ZAI_OK;
     if (H < 1 || R < 1 || R > 1024 || Dr < 0 || H > 65535 * LA_WARPS) return ZAI_BAD_SIZE;
     if (((size_t)LA_WARPS * (R + Dr) + (size_t)LA_KEYS * (R + Dr + 1)) * sizeof(float) > 200 * 1024) return ZAI_BAD_SIZE;
 #define LA_GO(MAXR)                                                                                                            \
     ZAI_DISPATCH(dtype, return (launch_latent<T, MAXR>(out, q_lat, q_rot, pages, block_table, table_width, positions, seq_idx, \
-                                                       page_size, N, H, R, Dr, scale, num_pages, status, stream)))
+                                                       page_size, N, H, R, Dr, scale, num_pages, status, sink, stream)))
     if (R <= 128) LA_GO(4);
     else if (R <= 256) LA_GO(8);
     else if (R <= 512) LA_GO(16);

@@ -144,3 +144,32 @@ ZAI_API int zai_add_rmsnorm(float* h, const void* delta, const float* gamma, voi
     const int threads = H >= 2048 ? 512 : 256;
     ZAI_DISPATCH(dtype, return launch_pdl(add_rmsnorm_kernel<T>, dim3(N), dim3(threads), 0, stream, h, (const T*)delta, gamma, (T*)out, eps, H));
 }
+
+// RMS norm of activation rows (not the residual stream): out[n, :] = x[n, :C] * rsqrt(mean(x^2) + eps) * gamma, the row
+// read from a column slice (row stride x_stride) in the activations' dtype, everything between in 32-bit.
+template <typename T>
+__global__ void rmsnorm_rows_kernel(T* __restrict__ out, const T* __restrict__ x, int x_stride, const float* __restrict__ gamma,
+                                    float eps, int C) {
+    __shared__ float red[33];
+    pdl_trigger();
+    pdl_wait();
+    const T* row = x + (size_t)blockIdx.x * x_stride;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        const float v = to_float(row[c]);
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)C + eps);
+    for (int c = threadIdx.x; c < C; c += blockDim.x)
+        out[(size_t)blockIdx.x * C + c] = from_float<T>(to_float(row[c]) * inv * (gamma ? gamma[c] : 1.f));
+}
+
+ZAI_API int zai_rmsnorm_rows(void* out, const void* x, int x_stride, int dtype, const float* gamma, float eps, int N, int C,
+                             cudaStream_t stream) {
+    if (N <= 0) return ZAI_OK;
+    if (C < 1 || x_stride < C) return ZAI_BAD_SIZE;
+    const int threads = C >= 1024 ? 256 : 128;
+    ZAI_DISPATCH(dtype, return launch_pdl(rmsnorm_rows_kernel<T>, dim3(N), dim3(threads), 0, stream, (T*)out, (const T*)x, x_stride,
+                                          gamma, eps, C));
+}

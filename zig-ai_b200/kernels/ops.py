@@ -32,7 +32,13 @@ _SIGNATURES = {
         "zai_gather_add_normed": [_P, _P, _P, _I, _P, _F, _P, _I, _I, _P],
     },
     "norm": {"zai_add_rmsnorm": [_P, _P, _P, _P, _I, _F, _I, _I, _P],
-             "zai_add_normed_rmsnorm": [_P, _P, _P, _F, _P, _P, _I, _F, _I, _I, _P]},
+             "zai_add_normed_rmsnorm": [_P, _P, _P, _F, _P, _P, _I, _F, _I, _I, _P],
+             "zai_rmsnorm_rows": [_P, _P, _I, _I, _P, _F, _I, _I, _P]},
+    "moe": {"zai_moe_route": [_P, _P, _P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _I, _P],
+            "zai_moe_max_tiles": [_I, _I, _I, _I],
+            "zai_moe_gather": [_P, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+            "zai_moe_gemm": [_P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _P],
+            "zai_moe_combine": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P]},
     "layernorm": {"zai_add_layernorm": [_P, _P, _P, _P, _P, _I, _F, _I, _I, _P]},
     "qkv_prepare": {
         "zai_qkv_prepare": [_P, _I, _I, _P, _P, _F, _I, _P, _I, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
@@ -40,9 +46,9 @@ _SIGNATURES = {
         "zai_sigmoid_gate": [_P, _P, ctypes.c_longlong, ctypes.c_longlong, _P, _I, _I, _I, _I, _I, _I, _P],
     },
     "latent_attention": {
-        "zai_latent_attention": [_P, _P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P],
+        "zai_latent_attention": [_P, _P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P],
         "zai_latent_attention_mma_supports": [_I, _I],
-        "zai_latent_attention_mma": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P],
+        "zai_latent_attention_mma": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P, _P],
     },
     "activation": {"zai_silu_mul": [_P, _P, _I, _I, _I, _P],
                    "zai_clamped_glu": [_P, _P, _I, _I, _I, _F, _F, _P],
@@ -54,12 +60,12 @@ _SIGNATURES = {
                                               _I, _P, _P, _P, _I, _I, _I, _P]},
     "min_gru": {"zai_min_gru": [_P, _P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P]},
     "gated_delta": {
-        "zai_delta_prepare": [_P, _P, _P, _I, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _F, _P],
-        "zai_gated_delta": [_P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
-        "zai_gated_rmsnorm": [_P, _P, _P, _P, _I, _I, _F, _I, _I, _I, _P],
+        "zai_delta_prepare": [_P, _P, _P, _P, _I, _P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _F, _P],
+        "zai_gated_delta": [_P, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+        "zai_gated_rmsnorm": [_P, _P, _P, _P, _I, _I, _F, _I, _I, _I, _I, _P],
         "zai_gated_delta_single_supports": [_I, _I],
-        "zai_gated_delta_single": [_P, _P, _I, _P, _P, _I, _P, _I, _I, _P, _P, _P, _F, _F, _P, _P, _I, _I, _I, _I, _I, _I, _I,
-                                   _P, _P],
+        "zai_gated_delta_single": [_P, _P, _I, _P, _I, _P, _I, _P, _I, _I, _P, _P, _P, _F, _F, _P, _P, _I, _I, _I, _I, _I, _I, _I,
+                                   _P, _I, _I, _P],
     },
     "shortconv": {"zai_short_conv": [_P, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P]},
     "rope_kv": {
@@ -1145,10 +1151,11 @@ def min_gru(zxg, b_z, b_x, state, step, write_state=True):
 
 @_timed("recurrence")
 def gated_delta(qkv, b, a, gate, a_log, dt_bias, norm_w, eps, state, step, heads, kv_heads, dim, vdim, write_state=True,
-                unit_eps=1e-6):
+                unit_eps=1e-6, channel_decay=False, gate_act="silu"):
     """The gated delta rule over the rows of a step.  qkv [N, 2 G D + H V] (q heads, k heads, v heads, after their
-    convolutions), b and a [N, H], gate [N, H V] (column slices are fine), state [slots, H, D, V] 32-bit.
-    Returns rms(o) * norm_w * silu(gate) per head, [N, H V] in qkv's dtype."""
+    convolutions), b [N, H], a [N, H] (with `channel_decay` [N, H D]: a decay per head and key channel, `dt_bias` as wide),
+    gate [N, H V] (column slices are fine), state [slots, H, D, V] 32-bit.
+    Returns rms(o) * norm_w * act(gate) per head (`gate_act`: silu or sigmoid), [N, H V] in qkv's dtype."""
     _cuda(a_log, dt_bias, norm_w, state)
     N = qkv.shape[0]
     H, G, D, V = int(heads), int(kv_heads), int(dim), int(vdim)
@@ -1156,7 +1163,9 @@ def gated_delta(qkv, b, a, gate, a_log, dt_bias, norm_w, eps, state, step, heads
     bp, bs = _rows_view(b)
     ap, as_ = _rows_view(a)
     gp, gs = _rows_view(gate)
-    if bs != as_ or state.dtype != torch.float32 or tuple(state.shape[1:]) != (H, D, V):
+    ch, act = int(bool(channel_decay)), {"silu": 0, "sigmoid": 1}[gate_act]
+    if (state.dtype != torch.float32 or tuple(state.shape[1:]) != (H, D, V) or a.shape[1] != (H * D if ch else H)
+            or dt_bias.numel() != a.shape[1] or b.shape[1] != H):
         raise KernelError("gated_delta: operands do not fit together")
     dev = qkv.device
     lib = "gated_delta"
@@ -1166,21 +1175,22 @@ def gated_delta(qkv, b, a, gate, a_log, dt_bias, norm_w, eps, state, step, heads
         # three kernels stream them as fast, measured within the spread between runs at 64 requests)
         out = torch.empty((N, H * V), dtype=qkv.dtype, device=dev)
         _check(_fn(lib, "zai_gated_delta_single")(
-            _ptr(out), qp, qs, bp, ap, bs, gp, gs, _dt(qkv), _ptr(a_log), _ptr(dt_bias), _ptr(norm_w), float(eps),
+            _ptr(out), qp, qs, bp, bs, ap, as_, gp, gs, _dt(qkv), _ptr(a_log), _ptr(dt_bias), _ptr(norm_w), float(eps),
             float(unit_eps), _ptr(state), _ptr(step.slot_ids), N, H, G, D, V, int(bool(write_state)), state.shape[0],
-            _status_ptr(dev), _stream()), "gated_delta_single")
+            _status_ptr(dev), ch, act, _stream()), "gated_delta_single")
         return out
     qk = torch.empty((N, 2, G, D), dtype=torch.float32, device=dev)
     bg = torch.empty((N, 2, H), dtype=torch.float32, device=dev)
+    gch = torch.empty((N, H, D), dtype=torch.float32, device=dev) if ch else None
     o = torch.empty((N, H * V), dtype=torch.float32, device=dev)
     out = torch.empty((N, H * V), dtype=qkv.dtype, device=dev)
-    _check(_fn(lib, "zai_delta_prepare")(_ptr(qk), _ptr(bg), qp, qs, bp, ap, bs, _dt(qkv), _ptr(a_log), _ptr(dt_bias), N, H, G, D,
-                                         float(unit_eps), _stream()), "delta_prepare")
+    _check(_fn(lib, "zai_delta_prepare")(_ptr(qk), _ptr(bg), _ptr(gch), qp, qs, bp, bs, ap, as_, _dt(qkv), _ptr(a_log), _ptr(dt_bias),
+                                         N, H, G, D, float(unit_eps), _stream()), "delta_prepare")
     vp = qp + 2 * G * D * qkv.element_size()
-    _check(_fn(lib, "zai_gated_delta")(_ptr(o), _ptr(qk), _ptr(bg), vp, qs, _dt(qkv), _ptr(state), _ptr(step.cu_q),
+    _check(_fn(lib, "zai_gated_delta")(_ptr(o), _ptr(qk), _ptr(bg), _ptr(gch), vp, qs, _dt(qkv), _ptr(state), _ptr(step.cu_q),
                                        _ptr(step.slot_ids), N, step.n_seqs, H, G, D, V, int(bool(write_state)), state.shape[0],
                                        _status_ptr(dev), _stream()), "gated_delta")
-    _check(_fn(lib, "zai_gated_rmsnorm")(_ptr(out), _ptr(o), _ptr(norm_w), gp, gs, _dt(qkv), float(eps), N, H, V, _stream()),
+    _check(_fn(lib, "zai_gated_rmsnorm")(_ptr(out), _ptr(o), _ptr(norm_w), gp, gs, _dt(qkv), float(eps), N, H, V, act, _stream()),
            "gated_rmsnorm")
     return out
 
@@ -1298,13 +1308,16 @@ USE_LATENT_MMA = os.environ.get("ZAI_LATENT_MMA", "1") == "1"
 
 
 @_timed("attention")
-def latent_attention(q_lat, q_rot, step, cache, heads, rank, rot_dim, scale, impl=None):
+def latent_attention(q_lat, q_rot, step, cache, heads, rank, rot_dim, scale, impl=None, sink=None):
     """Causal attention of every head against the cached rows [latent | rotated key part]: scores
     (q_lat . latent + q_rot . key part) * scale, output sum_j p_j latent_j, [N, H, rank].  bfloat16 with a rank
     that is a multiple of 32 and rank + rot_dim a multiple of 16 runs on the tensor cores (steps of many rows: the four
     warps of a block share the tiles of cached rows; steps of few rows: a warp a row and range of keys, the ranges added
-    up by a second kernel); everything else, and `impl="general"`, runs the general kernel."""
-    _cuda(q_lat, q_rot)
+    up by a second kernel); everything else, and `impl="general"`, runs the general kernel.  `sink` [H] 32-bit: one more
+    term exp(sink_h) in every row's denominator (no key, no value, not scaled)."""
+    _cuda(q_lat, q_rot, sink)
+    if sink is not None and (sink.dtype != torch.float32 or sink.numel() != int(heads)):
+        raise KernelError("latent_attention: the sink is one 32-bit number per head")
     N = q_lat.shape[0]
     H, R, Dr = int(heads), int(rank), int(rot_dim)
     pages, bt = cache.pages, cache.block_table
@@ -1325,11 +1338,12 @@ def latent_attention(q_lat, q_rot, step, cache, heads, rank, rot_dim, scale, imp
         _check(_fn("latent_attention", "zai_latent_attention_mma")(
             _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(q_lat), _ptr(q_rot), _ptr(pages), _ptr(bt), bt.shape[1],
             _ptr(step.positions), _ptr(step.seq_idx), cache.page_size, N, H, R, Dr, float(scale), split_keys, n_splits,
-            pages.shape[0], _status_ptr(q_lat.device), _stream()), "latent_attention_mma", 2 if n_splits > 1 else 1)
+            pages.shape[0], _status_ptr(q_lat.device), _ptr(sink), _stream()), "latent_attention_mma", 2 if n_splits > 1 else 1)
         return out
     _check(_fn("latent_attention", "zai_latent_attention")(
         _ptr(out), _ptr(q_lat), _ptr(q_rot), _ptr(pages), _dt(q_lat), _ptr(bt), bt.shape[1], _ptr(step.positions), _ptr(step.seq_idx),
-        cache.page_size, N, H, R, Dr, float(scale), pages.shape[0], _status_ptr(q_lat.device), _stream()), "latent_attention")
+        cache.page_size, N, H, R, Dr, float(scale), pages.shape[0], _status_ptr(q_lat.device), _ptr(sink), _stream()),
+        "latent_attention")
     return out
 
 
@@ -1363,3 +1377,67 @@ def scale_softcap(logits, scale, cap):
     _check(_fn("activation", "zai_scale_softcap")(_ptr(logits), logits.numel(), float(scale), float(cap or 0.0), _stream()),
            "scale_softcap")
     return logits
+
+
+# ----------------------------------------------------------------------------- norm of activation rows, routed experts
+@_timed("norm")
+def rmsnorm_rows(x, w, eps):
+    """RMS norm of activation rows x [N, C] (a column slice is fine) with the 32-bit weight w (or None), computed in
+    32-bit, in x's dtype."""
+    _cuda(w)
+    xp, xs = _rows_view(x)
+    N, C = x.shape
+    if w is not None and (w.dtype != torch.float32 or w.numel() != C):
+        raise KernelError("rmsnorm_rows: the weight is 32-bit, one value a column")
+    out = torch.empty((N, C), dtype=x.dtype, device=x.device)
+    _check(_fn("norm", "zai_rmsnorm_rows")(_ptr(out), xp, xs, _dt(x), _ptr(w), float(eps), N, C, _stream()), "rmsnorm_rows")
+    return out
+
+
+MOE_TALL_TILE_ROWS = 32      # from this many rows per expert on average, tiles of 64 rows instead of 16 (bfloat16)
+
+
+@_timed("experts")
+def routed_experts(x, w_router, w_gate_up, w_down, top, renorm=False, weight_on="input"):
+    """A mixture of gated feed-forwards.  x [N, W]; w_router [E, W] 32-bit; w_gate_up [E, 2 F, W] (an expert's gate rows,
+    then its up rows); w_down [E, W, F].  Every row goes to the `top` experts with the largest sigmoid(x . w_router^T)
+    (32-bit); the scores are the weights (divided by their sum with `renorm`), applied to the expert's input or to its
+    output; the row's results are summed in 32-bit.  Nothing is read back to the host."""
+    _cuda(w_router, w_gate_up, w_down)
+    xp, xs = _rows_view(x)
+    N, W = x.shape
+    E, F = w_gate_up.shape[0], w_gate_up.shape[1] // 2
+    top = int(top)
+    if (w_router.dtype != torch.float32 or tuple(w_router.shape) != (E, W) or tuple(w_gate_up.shape) != (E, 2 * F, W)
+            or tuple(w_down.shape) != (E, W, F) or w_gate_up.dtype != x.dtype or w_down.dtype != x.dtype
+            or weight_on not in ("input", "output")):
+        raise KernelError("routed_experts: operands do not fit together")
+    dev, dt, lib = x.device, _dt(x), "moe"
+    out = torch.empty((N, W), dtype=x.dtype, device=dev)
+    if N == 0:
+        return out
+    tall = dt == _BF16 and W % 8 == 0 and F % 8 == 0 and N * top >= MOE_TALL_TILE_ROWS * E
+    TM = 64 if tall else 16
+    max_tiles = _fn(lib, "zai_moe_max_tiles")(N, top, E, TM)
+    if max_tiles < 0:
+        raise KernelError("routed_experts: too many rows")
+    meta = torch.empty((4 * N * top + E + max_tiles,), dtype=torch.int32, device=dev)
+    ids, rank, dest = meta[:N * top], meta[N * top:2 * N * top], meta[2 * N * top:3 * N * top]
+    wts = meta[3 * N * top:4 * N * top].view(torch.float32)
+    counts, tile_expert = meta[4 * N * top:4 * N * top + E], meta[4 * N * top + E:]
+    on_input = int(weight_on == "input")
+    _check(_fn(lib, "zai_moe_route")(_ptr(ids), _ptr(wts), _ptr(rank), _ptr(counts), xp, xs, dt, _ptr(w_router), N, W, E, top,
+                                     int(bool(renorm)), _stream()), "moe_route")
+    rows = max_tiles * TM
+    x_sorted = torch.empty((rows, W), dtype=x.dtype, device=dev)
+    _check(_fn(lib, "zai_moe_gather")(_ptr(x_sorted), _ptr(dest), _ptr(tile_expert), xp, xs, dt, _ptr(ids), _ptr(wts), _ptr(rank),
+                                      _ptr(counts), N, W, E, top, TM, max_tiles, on_input, _stream()), "moe_gather")
+    act = torch.empty((rows, F), dtype=x.dtype, device=dev)
+    _check(_fn(lib, "zai_moe_gemm")(_ptr(act), int(dt == _F32), _ptr(x_sorted), _ptr(w_gate_up), dt, _ptr(tile_expert), max_tiles,
+                                    TM, W, F, 1, _stream()), "moe_gemm (gate/up)")
+    y = torch.empty((rows, W), dtype=torch.float32, device=dev)
+    _check(_fn(lib, "zai_moe_gemm")(_ptr(y), 1, _ptr(act), _ptr(w_down), dt, _ptr(tile_expert), max_tiles, TM, F, W, 0, _stream()),
+           "moe_gemm (down)")
+    _check(_fn(lib, "zai_moe_combine")(_ptr(out), dt, _ptr(y), _ptr(dest), _ptr(wts), N, W, top, 1 - on_input, _stream()),
+           "moe_combine")
+    return out

@@ -172,6 +172,27 @@ class LazyNorm:
         return self._norm(ops, self.residual.data, self.delta)
 
 
+# --------------------------------------------------------------------------- stacked projections
+ROW_ALIGN = 8      # columns: 16 bytes of bfloat16, the widest vector access of the kernels that read column slices
+
+
+def stack_rows(mats, align: int = ROW_ALIGN):
+    """Stack matrices [O_i, K] that read the same input into one [sum O_i', K] matrix, so that one product makes all
+    their outputs, each O_i rounded up to a multiple of `align` with rows of zeros: every output's column slice then
+    starts on a 16-byte boundary (and so does every row of the product) whatever the sizes are.  Returns the matrix and
+    the first column of every output."""
+    import torch
+    rows, at, offsets = [], 0, []
+    for m in mats:
+        offsets.append(at)
+        rows.append(m)
+        pad = -m.shape[0] % align
+        if pad:
+            rows.append(torch.zeros((pad, m.shape[1]), dtype=m.dtype, device=m.device))
+        at += m.shape[0] + pad
+    return torch.cat(rows, dim=0).contiguous(), offsets
+
+
 # --------------------------------------------------------------------------- interfaces
 class Part:
     """Base of every part.  `params()` declares tensors by local name (the layer's prefix is put

@@ -11,23 +11,27 @@ from .base import FeedForward, ParamDecl, register_part
 
 
 class SwiGlu(FeedForward):
+    """`names` gives the three tensors' names (gate, up, down)."""
     accepts_lazy_input = True     # x goes straight into a product
     graph_safe = True      # forward launches kernels only; nothing is read back to the host
     kernel_libs = ("gemm_tc_pair",)       # gate/up products of many rows with the activation as their epilogue (bfloat16)
 
-    def __init__(self, hidden: int, ff_dim: int):
+    def __init__(self, hidden: int, ff_dim: int, names=None):
         self.hidden, self.ff_dim = int(hidden), int(ff_dim)
+        self.names = {"gate": "ffn_gate.weight", "up": "ffn_up.weight", "down": "ffn_down.weight", **(names or {})}
 
     def params(self):
+        nm = self.names
         return {
-            "ffn_gate.weight": ParamDecl((self.ff_dim, self.hidden)),
-            "ffn_up.weight": ParamDecl((self.ff_dim, self.hidden)),
-            "ffn_down.weight": ParamDecl((self.hidden, self.ff_dim)),
+            nm["gate"]: ParamDecl((self.ff_dim, self.hidden)),
+            nm["up"]: ParamDecl((self.ff_dim, self.hidden)),
+            nm["down"]: ParamDecl((self.hidden, self.ff_dim)),
         }
 
     def bind(self, tensors, dtype):
-        self.w_gate_up = torch.cat([tensors["ffn_gate.weight"], tensors["ffn_up.weight"]], dim=0).contiguous()
-        self.w_down = tensors["ffn_down.weight"]
+        nm = self.names
+        self.w_gate_up = torch.cat([tensors[nm["gate"]], tensors[nm["up"]]], dim=0).contiguous()
+        self.w_down = tensors[nm["down"]]
         self.dtype = dtype
 
     def forward(self, x, step):
@@ -90,6 +94,52 @@ class ClampedGlu(FeedForward):
         return ops.linear(ops.linear_clamped_glu(x, self.w_gate_up, self.ff_dim, self.limit, self.alpha), self.w_down)
 
 
+class RoutedExperts(FeedForward):
+    """A mixture of `experts` small SwiGLU feed-forwards, of which every token uses `top`:
+
+        s = sigmoid(x . Wr^T)                 router, 32-bit
+        chosen = the `top` experts with the largest s;   w_e = s_e   (divided by their sum with `renormalize`)
+        out = sum over chosen e of  down_e( silu(gate_e(w_e x)) * up_e(w_e x) )          weight_on="input"
+                                or  w_e down_e( silu(gate_e(x)) * up_e(x) )              weight_on="output"
+
+    Experts have no biases.  The router's matrix is kept in 32-bit.  `names`: "router", and "gate", "up", "down" with
+    `{e}` standing for the expert's number."""
+    accepts_lazy_input = False    # the router and the experts read the normed rows themselves
+    graph_safe = True             # routing stays on the device: forward launches kernels only
+    kernel_libs = ("moe",)
+
+    def __init__(self, hidden: int, ff_dim: int, experts: int, top: int, renormalize: bool = False, weight_on: str = "input",
+                 names=None):
+        self.hidden, self.ff_dim, self.experts, self.top = int(hidden), int(ff_dim), int(experts), int(top)
+        self.renormalize, self.weight_on = bool(renormalize), weight_on
+        if not 1 <= self.top <= self.experts or self.top > 32:
+            raise ValueError(f"a token uses between 1 and min(experts, 32) experts, not {self.top} of {self.experts}")
+        if weight_on not in ("input", "output"):
+            raise ValueError("weight_on is 'input' or 'output'")
+        self.names = {"router": "ffn_router.weight", "gate": "ffn_gate.{e}.weight", "up": "ffn_up.{e}.weight",
+                      "down": "ffn_down.{e}.weight", **(names or {})}
+
+    def params(self):
+        nm, p = self.names, {self.names["router"]: ParamDecl((self.experts, self.hidden), "vector", init="conv")}
+        for e in range(self.experts):
+            p[nm["gate"].format(e=e)] = ParamDecl((self.ff_dim, self.hidden))
+            p[nm["up"].format(e=e)] = ParamDecl((self.ff_dim, self.hidden))
+            p[nm["down"].format(e=e)] = ParamDecl((self.hidden, self.ff_dim))
+        return p
+
+    def bind(self, tensors, dtype):
+        nm, E = self.names, range(self.experts)
+        self.w_router = tensors[nm["router"]].float().contiguous()
+        self.w_gate_up = torch.stack([torch.cat([tensors[nm["gate"].format(e=e)], tensors[nm["up"].format(e=e)]], dim=0)
+                                      for e in E]).contiguous()                                  # [E, 2F, hidden]
+        self.w_down = torch.stack([tensors[nm["down"].format(e=e)] for e in E]).contiguous()   # [E, hidden, F]
+        self.dtype = dtype
+
+    def forward(self, x, step):
+        return step.ops.routed_experts(x, self.w_router, self.w_gate_up, self.w_down, self.top, self.renormalize, self.weight_on)
+
+
 register_part("feed_forward", "swiglu", SwiGlu)
+register_part("feed_forward", "routed_experts", RoutedExperts)
 register_part("feed_forward", "clamped_glu", ClampedGlu)
 register_part("feed_forward", "dense", DenseMlp)

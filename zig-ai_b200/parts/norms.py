@@ -11,17 +11,21 @@ from .base import LazyNorm, Norm, NormedTerm, ParamDecl, Residual, register_part
 
 
 class RmsNorm(Norm):
+    """`offset`: what is added to the stored weight before it multiplies (1 for a weight stored around zero:
+    `x / rms(x) * (1 + w)`); the sum is made once at load, in 32-bit."""
     graph_safe = True      # forward launches kernels only; nothing is read back to the host
 
-    def __init__(self, size: int, eps: float, weight: str):
-        self.size, self.eps, self.weight_name = int(size), float(eps), weight
+    def __init__(self, size: int, eps: float, weight: str, offset: float = 0.0):
+        self.size, self.eps, self.weight_name, self.offset = int(size), float(eps), weight, float(offset)
         self.weight = None
 
     def params(self):
-        return {self.weight_name: ParamDecl((self.size,), "vector", init="norm_weight")}
+        return {self.weight_name: ParamDecl((self.size,), "vector", init="norm_weight" if self.offset == 0.0 else "conv")}
 
     def bind(self, tensors, dtype):
         self.weight = tensors[self.weight_name]
+        if self.offset != 0.0:
+            self.weight = (self.weight.float() + self.offset).contiguous()
         self.dtype = dtype
 
     def forward(self, h, delta, step, lazy=False, rows=None):
