@@ -138,11 +138,16 @@ def gated_ff(h, w, p):
     return (silu(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T
 
 
-def routed_ff(h, mlp, w, p):
-    """Every token goes to its `top` experts by sigmoid score; an expert sees score * h."""
+def routed_ff(h, mlp, w, p, margins_out=None):
+    """Every token goes to its `top` experts by sigmoid score; an expert sees score * h.  `margins_out`: a list that
+    receives, per token, how far the last chosen expert's router logit lies above the first one not chosen."""
     E, top = mlp["router"]["experts"], mlp["router"]["top"]
-    s = torch.sigmoid(h @ w[p + "router"].T)                       # [T, E]
+    z = h @ w[p + "router"].T                                      # [T, E]
+    s = torch.sigmoid(z)
     chosen = torch.topk(s, top, dim=-1).indices
+    if margins_out is not None:
+        zs = z.sort(dim=-1, descending=True).values
+        margins_out.append(zs[:, top - 1] - zs[:, top] if top < E else torch.full((h.shape[0],), math.inf, dtype=F64))
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e in chosen[t].tolist():
@@ -150,17 +155,18 @@ def routed_ff(h, mlp, w, p):
     return out
 
 
-def feed_forward(h, mlp, w, p):
+def feed_forward(h, mlp, w, p, margins_out=None):
     if mlp["kind"] == "dense":
         return gated_ff(h, w, p)
     if mlp["kind"] == "moe":
-        return routed_ff(h, mlp, w, p)
+        return routed_ff(h, mlp, w, p, margins_out)
     raise ValueError(mlp["kind"])
 
 
 # ----------------------------------------------------------------------------- the model
-def forward(cfg, w, tokens, layers_out=None):
-    """Logits [T, vocab] of one sequence.  `layers_out`: a list that receives the stream after every layer."""
+def forward(cfg, w, tokens, layers_out=None, margins_out=None):
+    """Logits [T, vocab] of one sequence.  `layers_out`: a list that receives the stream after every layer;
+    `margins_out`: one that receives every routed layer's margins (see routed_ff)."""
     eps = cfg["norm"]["eps"]
     x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)] * cfg["embedding"]["scale"]
     for i, layer in enumerate(cfg["layers"]):
@@ -174,7 +180,7 @@ def forward(cfg, w, tokens, layers_out=None):
         else:
             raise ValueError(layer["type"])
         if layer.get("mlp") is not None:
-            x = x + feed_forward(offset_norm(x, w[p + "norm2"], eps), layer["mlp"], w, p + "mlp.")
+            x = x + feed_forward(offset_norm(x, w[p + "norm2"], eps), layer["mlp"], w, p + "mlp.", margins_out)
         if layers_out is not None:
             layers_out.append(x.clone())
     return offset_norm(x, w["final.norm"], eps) @ w["head"].T

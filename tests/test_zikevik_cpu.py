@@ -252,7 +252,7 @@ def test_the_routers_weight_scales_the_experts_input(models):
     toks = tokens(cfg["vocab"], 50, 73)
     want = P.forward(cfg, W, toks)
 
-    def on_output(h, mlp, w, p):
+    def on_output(h, mlp, w, p, margins_out=None):
         s = torch.sigmoid(h @ w[p + "router"].T)
         out = torch.zeros_like(h)
         for t in range(h.shape[0]):
