@@ -248,6 +248,8 @@ def run_ours(args):
         return run_vunolorn(args)
     if args.only == "pikasun":
         return run_pikasun(args)
+    if args.only == "zikevik":
+        return run_zikevik(args)
     if args.only == "long":
         return run_long(args)
     if args.only == "sample":
@@ -373,7 +375,19 @@ def engine_numbers(eng):
         matrix += sum(numel(d.shape) for d in decls.values() if d.role == "table")
     cache = eng.runner.cache
     state = sum(len(g.members) * numel(g.need.shape) * 4 for g in cache.groups if not g.paged)
-    return dict(matrix_params=matrix, kv_bytes_per_token=cache.bytes_per_token(), state_bytes=state)
+    routed = []        # (experts, experts a token uses, parameters of one expert) of every mixture of experts
+    for blk in eng.runner.model.blocks:
+        ff = getattr(blk, "feed_forward", None)
+        if ff is not None and hasattr(ff, "experts") and hasattr(ff, "top"):
+            routed.append((ff.experts, ff.top, 3 * ff.hidden * ff.ff_dim))
+    return dict(matrix_params=matrix, kv_bytes_per_token=cache.bytes_per_token(), state_bytes=state, routed=routed)
+
+
+def params_read(nums, tokens):
+    """Matrix parameters that a step of `tokens` rows reads: everything but the experts that none of its rows chose
+    (expected, for rows that choose independently and evenly)."""
+    unread = sum(E * (1.0 - top / E) ** tokens * per for E, top, per in nums["routed"])
+    return nums["matrix_params"] - unread
 
 
 def kernel_classes(eng, entries):
@@ -658,6 +672,177 @@ def run_pikasun(args):
                 del eng
                 torch.cuda.empty_cache()
         kernels += pikasun_kernel_rooflines(width, hbm_peak, flops_peak)
+    for r in kernels:
+        print(json.dumps(r), flush=True)
+    print(f"\npeaks ({peak_src}): {hbm_peak:.0f} GB/s copy bandwidth, {flops_peak:.0f} TFLOP/s bf16 product (burst)\n")
+    print("| model | point | ms a step (device) | tokens/s (device) | tokens/s (end to end) | of the copy peak | launches a step |")
+    print("|---|---|---|---|---|---|---|")
+    for r in rows:
+        print(f"| {r['model']} | {r['point']} | {r['ms']} | {r['tokens_per_s']} | {r.get('e2e_tokens_per_s', '')} | "
+              f"{r.get('frac_of_copy_peak', '')} | {r.get('launches_per_step', '')} |")
+    print("\n| kernel | point | width | us | GFLOP | TFLOP/s | of the tensor peak | MB | GB/s | of the copy peak |")
+    print("|---|---|---|---|---|---|---|---|---|---|")
+    for r in kernels:
+        print(f"| {r['kernel']} | {r['point']} | {r['width']} | {r['us']} | {r['GFLOP']} | {r['TFLOP_per_s']} | {r['of_tensor_peak']} | "
+              f"{r['MB']} | {r['GB_per_s']} | {r['of_copy_peak']} |")
+    return 0
+
+
+# ----------------------------------------------------------------------------- the Zikevik design beside Pikasun
+def zikevik_config(width, layers=16, vocab=65536):
+    """A Zikevik model of a real model's proportions: groups of four layers (a delta rule with a decay per key channel in
+    front of a dense feed-forward; latent attention in front of eight experts of which a token uses two; latent attention
+    in front of a dense feed-forward; the delta rule in front of the experts).  Head size 64, value heads of 128 in the
+    delta rule, latents of rank 256 for keys/values and 384 for queries, a rotated part of 32.  A token's two experts hold
+    as many parameters as the dense feed-forward of three times the width."""
+    heads = width // 64
+    dense = {"kind": "dense", "ff": 3 * width}
+    moe = {"kind": "moe", "expert": {"ff": 3 * width // 2}, "router": {"experts": 8, "top": 2}}
+    delta = {"heads": heads, "kv_heads": heads // 2, "dim": 64, "vdim": 128, "conv": 4, "decay_rank": width // 16, "gate_rank": width // 8}
+    latent = {"heads": heads, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 256, "q_rank": 384, "scale": 96 ** -0.5,
+              "rot": {"base": 10000.0, "dims": 32}}
+    group = [("channel_delta", delta, dense), ("latent_attention", latent, moe), ("latent_attention", latent, dense),
+             ("channel_delta", delta, moe)]
+    return {"architecture": "Zikevik", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+            "layers": [{"type": t, "mixer": dict(m), "mlp": dict(f)} for t, m, f in (group[i % 4] for i in range(layers))]}
+
+
+def zikevik_kernel_rooflines(width, hbm_peak, flops_peak):
+    """Every kernel that the design adds, alone at the sizes of `zikevik_config(width)`, beside the like kernel of the
+    closest existing design at the same sizes: the delta rule with a decay per key channel beside the one with a decay
+    per head (Vunolorn's); latent attention with a sink beside the one without (Pikasun's); the routed experts beside a
+    dense gated feed-forward with a token's share of their parameters; the norm of activation rows beside the residual
+    norm.  A portion of 2048 tokens and 64 single tokens (over contexts of 2048 where there is one), timed with CUDA
+    events, the L2 flushed before every call."""
+    import torch
+    from zig_ai_b200.cache.manager import CacheView
+    from zig_ai_b200.engine.batch import pack_step
+    from zig_ai_b200.kernels import ops
+    ops.require(torch.bfloat16, ("latent_attention", "qkv_prepare", "causal_conv", "gated_delta", "moe"))
+    dev, dt = torch.device("cuda"), torch.bfloat16
+    H, G, D, V, R, Dr, Rq, ps = width // 64, width // 128, 64, 128, 256, 32, 384, 64
+    E, top, F = 8, 2, 3 * width // 2
+    g = torch.Generator().manual_seed(1)
+    rnd = lambda *shape, s=1.0: (torch.randn(*shape, generator=g) * s).to(dt).to(dev)
+    rows = []
+
+    def step_of(ctx, q_lens):
+        spans, tables, at = [], [], 1
+        width_pages = max(-(-(c + n) // ps) for c, n in zip(ctx, q_lens))
+        for s_, (c, n) in enumerate(zip(ctx, q_lens)):
+            need = -(-(c + n) // ps)
+            tables.append(list(range(at, at + need)) + [0] * (width_pages - need))
+            at += need
+            spans.append((s_, c, [0] * n, [], s_ + 1))
+        return pack_step(ops, dt, dev, spans, {0: tables}), at
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timed(fn, reps=10):
+        for _ in range(3):
+            fn()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        total = 0.0
+        for _ in range(reps):
+            flush.zero_()                                    # larger than L2: the timed call starts cold
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            total += a.elapsed_time(b)
+        return total / reps
+
+    for point, ctx, q_lens in (("2048-token portion", [0], [2048]), ("64 single tokens, context 2048", [2047] * 64, [1] * 64)):
+        step, n_pages = step_of(ctx, q_lens)
+        N, B = sum(q_lens), len(q_lens)
+        # the delta rule: norms and gates, the recurrence, the output norm
+        cols = 2 * G * D + H * V
+        qkv, gate, b = rnd(N, cols), rnd(N, H * V), rnd(N, H)
+        a_ch, a_hd = rnd(N, H * D), rnd(N, H)
+        state = torch.zeros(B + 1, H, D, V, device=dev)
+        al, nw = torch.zeros(H, device=dev), torch.ones(V, device=dev)
+        by = N * (cols + 2 * H * V + H) * 2 + B * H * D * V * 8
+        ms = timed(lambda: ops.gated_delta(qkv, b, a_ch, gate, al, torch.zeros(H * D, device=dev), nw, 1e-6, state, step, H, G, D, V,
+                                           channel_decay=True, gate_act="sigmoid"))
+        rows.append(("delta rule, a decay per key channel", point, ms, 0.0, by + N * H * D * 2))
+        ms = timed(lambda: ops.gated_delta(qkv, b, a_hd, gate, al, torch.zeros(H, device=dev), nw, 1e-6, state, step, H, G, D, V))
+        rows.append(("delta rule, a decay per head (Vunolorn's)", point, ms, 0.0, by + N * H * 2))
+        # latent attention
+        keys = sum((c + n) * n - n * (n - 1) // 2 for c, n in zip(ctx, q_lens))           # (query, key) pairs
+        cached = sum(c + n for c, n in zip(ctx, q_lens))
+        view = CacheView(0, rnd(n_pages, ps, R + Dr, s=0.3), step.block_tables[0], ps)
+        q_lat, q_rot, sink = rnd(N, H, R), rnd(N, H, Dr), torch.zeros(H, device=dev)
+        fl, by = 2.0 * keys * H * (2 * R + Dr), cached * (R + Dr) * 2 + N * H * (2 * R + Dr) * 2
+        for label, sk in (("latent attention with a sink", sink), ("latent attention (Pikasun's)", None)):
+            rows.append((label, point, timed(lambda: ops.latent_attention(q_lat, q_rot, step, view, H, R, Dr, 0.1, sink=sk)), fl, by))
+        # the feed-forwards
+        x = rnd(N, width)
+        w_router = (torch.randn(E, width, generator=g) * 0.05).to(dev)
+        w_gu, w_dn = rnd(E, 2 * F, width, s=0.02), rnd(E, width, F, s=0.02)
+        used = min(E, N * top)
+        rows.append((f"routed experts ({top} of {E})", point, timed(lambda: ops.routed_experts(x, w_router, w_gu, w_dn, top)),
+                     2.0 * N * top * 3 * width * F, used * 3 * width * F * 2 + N * width * 4))
+        d_gu, d_dn = rnd(2 * top * F, width, s=0.02), rnd(width, top * F, s=0.02)
+        rows.append(("dense gated feed-forward of a token's share", point,
+                     timed(lambda: ops.linear(ops.linear_swiglu(x, d_gu, top * F), d_dn)), 2.0 * N * 3 * width * top * F,
+                     3 * width * top * F * 2 + N * width * 4))
+        # norms
+        y = rnd(N, Rq + H + R + Dr + 8)
+        wq = torch.ones(Rq, device=dev)
+        rows.append(("norm of activation rows (the query latent)", point, timed(lambda: ops.rmsnorm_rows(y[:, :Rq], wq, 1e-6)), 0.0, N * Rq * 4))
+        h, delta_ = torch.randn(N, width, generator=g).to(dev), rnd(N, width)
+        w1 = torch.ones(width, device=dev)
+        rows.append(("RMS norm + residual (shared with LFM2)", point, timed(lambda: ops.add_rmsnorm(h, delta_, w1, 1e-6, dt)), 0.0, N * width * 12))
+    return [{"kernel": k, "point": p, "width": width, "us": round(ms * 1e3, 2), "GFLOP": round(fl / 1e9, 2), "MB": round(by / 1e6, 2),
+             "TFLOP_per_s": round(fl / ms / 1e9, 1), "of_tensor_peak": round(fl / ms / 1e9 / flops_peak, 4),
+             "GB_per_s": round(by / ms / 1e6, 1), "of_copy_peak": round(by / ms / 1e6 / hbm_peak, 4)} for k, p, ms, fl, by in rows]
+
+
+def run_zikevik(args):
+    """Prefill and decode throughput of the Zikevik design at two widths beside the Pikasun design (the closest one:
+    latent attention in front of gated feed-forwards) of the same width, layer count and vocabulary; the time of a prefill
+    and of a decode step by kernel class; and its kernels alone beside the like kernels.  JSON lines, then markdown."""
+    import torch
+    import zig_ai_b200 as z
+    from zig_ai_b200.config import config_from_dict
+    hbm_peak, flops_peak, peak_src = peaks()
+    rows, classes, kernels = [], [], []
+    for width in (1024, 2048):
+        for label, cfg_dict in ((f"Zikevik-{width}", zikevik_config(width)), (f"Pikasun-{width}", pikasun_config(width))):
+            cfg = config_from_dict(cfg_dict)
+            with tempfile.TemporaryDirectory(prefix="bench_zikevik_") as d:
+                z.write_random_model(cfg, 0, d)
+                eng = z.Engine(d, "bfloat16", max_num_seqs=64, max_batched_tokens=2048 + 64, max_model_len=CONTEXT,
+                               max_tokens=64 * CONTEXT, page_size=args.page_size)
+                nums = engine_numbers(eng)
+                active = params_read(nums, 1)
+                prefill_ms = time_prefill(eng, reps=5)
+                T = PREFILL_TOKENS
+                rows.append({"model": label, "width": width, "matrix_params_M": round(nums["matrix_params"] / 1e6, 1),
+                             "active_params_M": round(active / 1e6, 1), "point": "prefill 2048", "ms": round(prefill_ms, 3),
+                             "tokens_per_s": round(T / prefill_ms * 1e3),
+                             "matrix_TFLOP_per_s": round(2 * T * active / prefill_ms / 1e9, 1)})
+                print(json.dumps(rows[-1]), flush=True)
+                for B in (1, 8, 64):
+                    dev_ms, e2e_ms, ctx_tokens, launches, _, _, _ = time_decode(eng, B, max(min(args.steps, 100), 20), args.warmup)
+                    read = params_read(nums, B)       # of the experts, a step reads those that its tokens chose
+                    step_bytes = 2 * read + ctx_tokens * nums["kv_bytes_per_token"] + 2 * B * nums["state_bytes"]
+                    rows.append({"model": label, "width": width, "point": f"decode batch {B}", "ms": round(dev_ms, 4),
+                                 "e2e_ms": round(e2e_ms, 4), "tokens_per_s": round(B / dev_ms * 1e3),
+                                 "e2e_tokens_per_s": round(B / e2e_ms * 1e3), "GB_a_step": round(step_bytes / 1e9, 3),
+                                 "frac_of_copy_peak": round(step_bytes / (dev_ms * 1e-3) / 1e9 / hbm_peak, 3),
+                                 "launches_per_step": round(launches)})
+                    print(json.dumps(rows[-1]), flush=True)
+                g = random.Random(5)
+                V = eng.config.vocab_size
+                eng.flush()
+                pre = kernel_classes(eng, [("kc", [g.randrange(V) for _ in range(T)], [T - 1])])
+                dec = kernel_classes(eng, [(f"kc{i}", [g.randrange(V)], [0]) for i in range(64)])
+                classes.append({"model": label, "prefill_2048_ms_by_class": pre, "decode_64_first_token_ms_by_class": dec})
+                print(json.dumps(classes[-1]), flush=True)
+                del eng
+                torch.cuda.empty_cache()
+        kernels += zikevik_kernel_rooflines(width, hbm_peak, flops_peak)
     for r in kernels:
         print(json.dumps(r), flush=True)
     print(f"\npeaks ({peak_src}): {hbm_peak:.0f} GB/s copy bandwidth, {flops_peak:.0f} TFLOP/s bf16 product (burst)\n")
@@ -1027,9 +1212,9 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "gemm", "timeline", "table", "stream", "long", "sample", "vunolorn", "pikasun"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "gemm", "timeline", "table", "stream", "long", "sample", "vunolorn", "pikasun", "zikevik"],
                     help="profiling aid: run only the batch-8 decode steps or only the prefill (prints a short line); "
-                         "table: every figure of the 350M, 700M and 1.2B shapes (profiles/measurements.md); pikasun: the Pikasun design beside LFM2 at equal width; vunolorn: the "
+                         "table: every figure of the 350M, 700M and 1.2B shapes (profiles/measurements.md); pikasun: the Pikasun design beside LFM2 at equal width; zikevik: the Zikevik design beside Pikasun at equal width, and its kernels beside the like ones; vunolorn: the "
                          "Vunolorn hybrid at two widths beside LFM2 at equal width, and its recurrent kernels alone")
     ap.add_argument("--batch", type=int, default=8, help="with --only decode: the batch size; with --only stream: 24, 64 or "
                                                          "128 runs that row count only")

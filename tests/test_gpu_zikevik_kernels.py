@@ -21,7 +21,7 @@ DTYPES = [torch.float32, torch.bfloat16]
 
 def ops():
     from zig_ai_b200.kernels import ops as o
-    o.require(extra=("causal_conv", "gated_delta", "latent_attention", "qkv_prepare", "moe"))
+    o.require(extra=("causal_conv", "gated_delta", "latent_attention", "qkv_prepare", "moe", "gemm_tc"))
     return o
 
 
@@ -158,7 +158,8 @@ def expert_tensors(g, E, F, W, dtype):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("weight_on,renorm", [("input", False), ("output", False), ("input", True), ("output", True)])
 @pytest.mark.parametrize("N,W,F,E,top", [(1, 64, 24, 5, 2), (7, 40, 20, 9, 1), (33, 66, 16, 7, 7), (70, 128, 64, 8, 2), (300, 192, 96, 8, 1),
-                                         (600, 256, 136, 4, 2), (5, 50, 12, 3, 3), (40, 320, 128, 1, 1), (130, 96, 40, 40, 6)])
+                                         (600, 256, 136, 4, 2), (5, 50, 12, 3, 3), (40, 320, 128, 1, 1), (130, 96, 40, 40, 6), (1500, 128, 72, 3, 2),
+                                         (2100, 64, 24, 16, 1), (900, 200, 328, 2, 2)])
 def test_routed_experts(dtype, weight_on, renorm, N, W, F, E, top):
     o = ops()
     g = torch.Generator().manual_seed(17)
@@ -171,24 +172,33 @@ def test_routed_experts(dtype, weight_on, renorm, N, W, F, E, top):
     # a row whose top scores lie closer together than the router's rounding may go to another expert in the two versions
     s = torch.sigmoid(x.float() @ w_router.t()).sort(dim=-1, descending=True).values
     sure = torch.ones(N, dtype=torch.bool, device="cuda") if top == E else (s[:, top - 1] - s[:, top]) > 1e-4
-    assert int(sure.sum()) >= N - 2
+    assert int(sure.sum()) >= N - max(2, N // 100)
     assert torch.allclose(a.float()[sure], b.float()[sure], **tol(dtype))
     assert o.read_status() == 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_a_rows_experts_do_not_depend_on_the_other_rows(dtype):
+def test_a_rows_experts_do_not_depend_on_the_other_rows(dtype, monkeypatch):
     """The same rows alone, among few others and among many (other tile heights, other places in the sorted layout):
-    bit for bit the same results."""
+    bit for bit the same results from the kernels that share an order of summation (tiles of 16 and of 64 rows), and
+    from the grouped tensor-core products whatever else the step holds; between the two, equal within rounding."""
     o = ops()
     g = torch.Generator().manual_seed(19)
     W, F, E, top = 128, 64, 8, 2
     w_router, w_gate_up, w_down = expert_tensors(g, E, F, W, dtype)
     x = torch.randn(700, W, generator=g).to(dtype).cuda()
+    many = o.routed_experts(x, w_router, w_gate_up, w_down, top)                 # bfloat16: the grouped products
+    perm = torch.randperm(700, generator=g).cuda()
+    assert torch.equal(o.routed_experts(x[perm].contiguous(), w_router, w_gate_up, w_down, top), many[perm])
+    half = o.routed_experts(x[:400].contiguous(), w_router, w_gate_up, w_down, top)
+    assert torch.equal(half, many[:400])
+    monkeypatch.setattr(o, "USE_MOE_GROUPED_TC", False)
     all_rows = o.routed_experts(x, w_router, w_gate_up, w_down, top)
+    assert torch.allclose(all_rows.float(), many.float(), **tol(dtype))
     for rows in ([0], [3, 4, 5], list(range(100, 140)), list(range(690, 700)) + list(range(10))):
         part = o.routed_experts(x[rows].contiguous(), w_router, w_gate_up, w_down, top)
         assert torch.equal(part, all_rows[rows]), rows[:3]
+    assert o.read_status() == 0
 
 
 def test_the_router_picks_the_largest_scores_and_the_lower_index_of_equals():

@@ -22,6 +22,9 @@
 //                      apply the epilogue and store
 // Blocks are persistent (one per SM, tiles taken round robin) and TMEM holds the accumulators of two
 // tiles, so a tile's epilogue overlaps the next tile's products.
+// Grouped products (a mixture of experts): the rows are sorted by group, every group's rows start at a multiple of
+// 128, W holds one matrix per group and a table in device memory names the group of every token tile; the
+// producer adds the group's first row to the weight tile's coordinate, and nothing else changes.
 // TMA loads are never multicast.  Every wait on an mbarrier is bounded: when it runs out the block
 // raises an error word in global memory, every role leaves its loop, TMEM is freed and the block
 // returns; the host reports the error.
@@ -90,7 +93,13 @@ struct TcArgs {
     int F;                // SwiGLU: gate rows 0..F-1, up rows F..2F-1
     int stages;
     int tiles_o, tiles;   // tiles along the weight rows; all tiles (tile t: o tile t % tiles_o, token tile t / tiles_o)
+    // Grouped products: W holds one matrix per group, `group_rows` rows each, and token tile i takes the matrix of
+    // group tile_group[i]; a token tile whose group is negative is skipped by every role.  nullptr: one matrix.
+    const int* tile_group;
+    int group_rows;
 };
+
+__device__ __forceinline__ int tc_group_of(const TcArgs& a, int t) { return a.tile_group ? a.tile_group[t / a.tiles_o] : 0; }
 
 // Blocks are persistent: block b takes tiles b, b + gridDim.x, ...  The accumulator memory holds two
 // tiles, so the epilogue of one tile runs while the products of the next are issued.
@@ -142,15 +151,18 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
             int issued = 0, it = 0;                            // `it` counts k-blocks over all of this block's tiles
             bool ok = true;
             for (int t = blockIdx.x; t < a.tiles && ok; t += gridDim.x) {
+                const int grp = tc_group_of(a, t);
+                if (grp < 0) continue;
                 const int o0 = (t % a.tiles_o) * TC_BM, n0 = (t / a.tiles_o) * BN;
+                const int w0 = grp * a.group_rows + o0;        // (a tile that runs past its matrix reads rows that the epilogue drops)
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % stages;
                     const uint32_t ph = (it / stages) & 1;
                     if (!mbar_wait(&empty_bar[s], ph ^ 1, failed)) { ok = false; break; }
                     unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
                     mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-                    tma_load_2d(st, &map_w, kb * TC_BK, o0, &full_bar[s]);
-                    if (NA == 2) tma_load_2d(st + A_BYTES, &map_w, kb * TC_BK, a.F + o0, &full_bar[s]);
+                    tma_load_2d(st, &map_w, kb * TC_BK, w0, &full_bar[s]);
+                    if (NA == 2) tma_load_2d(st + A_BYTES, &map_w, kb * TC_BK, a.F + w0, &full_bar[s]);
                     tma_load_2d(st + NA * A_BYTES, &map_x, kb * TC_BK, n0, &full_bar[s]);
                     issued = it + 1;
                 }
@@ -174,8 +186,10 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
             // instruction descriptor: D fp32, A and B bfloat16, both K-major, N = BN, M = 128
             constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
             bool ok = true;
-            int it = 0, local = 0;
-            for (int t = blockIdx.x; t < a.tiles && ok; t += gridDim.x, ++local) {
+            int it = 0, local = -1;                            // `local` counts the tiles that this block runs
+            for (int t = blockIdx.x; t < a.tiles && ok; t += gridDim.x) {
+                if (tc_group_of(a, t) < 0) continue;
+                ++local;
                 const int buf = local % ACC_BUFS;
                 const uint32_t acc = tmem_base + buf * TILE_COLS;
                 // the epilogue must have drained this buffer (ACC_BUFS tiles ago)
@@ -205,8 +219,10 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
         const int q = warp & 3;                                // this warp's quarter of the TMEM lanes
         const int row = q * 32 + lane;
         const int o_limit = EPI == TC_EPI_SWIGLU ? a.F : a.O;
-        int local = 0;
-        for (int t = blockIdx.x; t < a.tiles; t += gridDim.x, ++local) {
+        int local = -1;
+        for (int t = blockIdx.x; t < a.tiles; t += gridDim.x) {
+            if (tc_group_of(a, t) < 0) continue;
+            ++local;
             const int buf = local % ACC_BUFS;
             const int o = (t % a.tiles_o) * TC_BM + row, n0 = (t / a.tiles_o) * BN;
             if (!mbar_wait(&acc_full_bar[buf], (local / ACC_BUFS) & 1, failed) || *failed) break;
@@ -342,6 +358,7 @@ ZAI_API int zai_gemm_tc(void* y, const void* W, const void* x, int* status, int 
     a.F = O / 2;
     a.ldy = epilogue == TC_EPI_SWIGLU ? O / 2 : O;
     a.stages = 0; a.tiles_o = 0; a.tiles = 0;
+    a.tile_group = nullptr; a.group_rows = 0;
     const int o_tiles = ((epilogue == TC_EPI_SWIGLU ? a.F : O) + TC_BM - 1) / TC_BM;
 #define TC_CASE(BNV, EPIV, BUFS) if (bn == BNV && epilogue == EPIV) return tc_launch<BNV, EPIV, BUFS>(mw, mx, a, o_tiles, stream);
     TC_CASE(128, TC_EPI_BF16, 2) TC_CASE(256, TC_EPI_BF16, 2)
@@ -349,4 +366,31 @@ ZAI_API int zai_gemm_tc(void* y, const void* W, const void* x, int* status, int 
     TC_CASE(128, TC_EPI_SWIGLU, 2) TC_CASE(256, TC_EPI_SWIGLU, 1)
 #undef TC_CASE
     return ZAI_BAD_SIZE;
+}
+
+// Grouped products over rows sorted by group: x [n_tiles * 128, K]; W [groups, O, K]; token tile i (128 rows) takes the
+// matrix of group tile_group[i] (device memory; negative: the tile is skipped and its rows of y stay as they are).
+// Epilogues as above: y [n_tiles * 128, O] bfloat16 or 32-bit, or with SwiGLU [n_tiles * 128, O / 2].
+ZAI_API int zai_gemm_tc_grouped(void* y, const void* W, const void* x, const int* tile_group, int* status, int n_tiles, int groups,
+                                int O, int K, int epilogue, cudaStream_t stream) {
+    if (n_tiles <= 0) return ZAI_OK;
+    const long long rows = (long long)n_tiles * 128, w_rows = (long long)groups * O;
+    if (groups < 1 || rows > 0x7fffffff || w_rows > 0x7fffffff || !zai_gemm_tc_supports((int)rows, O, K, epilogue)) return ZAI_BAD_SIZE;
+    if (epilogue != TC_EPI_BF16 && epilogue != TC_EPI_F32 && epilogue != TC_EPI_SWIGLU) return ZAI_BAD_SIZE;
+    if ((reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(x) & 15) || !tile_group) return ZAI_BAD_SIZE;
+    CUtensorMap mw, mx;
+    int e = make_map(&mw, W, (int)w_rows, K, TC_BM);
+    if (e) return e;
+    e = make_map(&mx, x, (int)rows, K, 128);
+    if (e) return e;
+    TcArgs a;
+    a.y = y; a.status = status; a.N = (int)rows; a.O = O; a.K = K;
+    a.F = O / 2;
+    a.ldy = epilogue == TC_EPI_SWIGLU ? O / 2 : O;
+    a.stages = 0; a.tiles_o = 0; a.tiles = 0;
+    a.tile_group = tile_group; a.group_rows = O;
+    const int o_tiles = ((epilogue == TC_EPI_SWIGLU ? a.F : O) + TC_BM - 1) / TC_BM;
+    if (epilogue == TC_EPI_BF16) return tc_launch<128, TC_EPI_BF16, 2>(mw, mx, a, o_tiles, stream);
+    if (epilogue == TC_EPI_F32) return tc_launch<128, TC_EPI_F32, 2>(mw, mx, a, o_tiles, stream);
+    return tc_launch<128, TC_EPI_SWIGLU, 2>(mw, mx, a, o_tiles, stream);
 }

@@ -13,7 +13,8 @@
 //     expert of every tile;
 //   * two grouped products over that layout (gate|up with the activation as epilogue, then down): a block owns a
 //     tile of TM rows x 64 output columns of one expert; bfloat16 on the tensor cores (mma.sync m16n8k16, cp.async
-//     ring of three stages), any other case by 32-bit multiply-adds;
+//     ring of three stages), any other case by 32-bit multiply-adds.  Steps with many rows an expert gather with a
+//     tile height of 128 and run both products in the grouped mode of the tcgen05 kernel (gemm_tc.cu) instead;
 //   * combine: a row's `top` results summed in 32-bit in the order of the choice and rounded once.
 // A row's result depends on the row alone: on which tile it lands, what else the tile holds and in which order the
 // counter was taken changes nothing, since every output element is a sum over k in a fixed order.
@@ -311,7 +312,7 @@ ZAI_API int zai_moe_gather(void* xs, int* dest, int* tile_expert, const void* x,
                            int scale_input, cudaStream_t stream) {
     if (N <= 0) return ZAI_OK;
     const long long items = (long long)N * top;
-    if (items >= 0x7fffffff || (TM != 16 && TM != 64) || (long long)max_tiles * TM >= (1 << 24)) return ZAI_BAD_SIZE;
+    if (items >= 0x7fffffff || (TM != 16 && TM != 64 && TM != 128) || (long long)max_tiles * TM >= (1 << 24)) return ZAI_BAD_SIZE;
     ZAI_DISPATCH(dtype, return launch_pdl(moe_gather_kernel<T>, dim3((unsigned)items + 1), dim3(128), 0, stream, (T*)xs, dest,
                                           tile_expert, (const T*)x, x_stride, ids, wts, rank, counts, (int)items, W, E, top, TM,
                                           max_tiles, scale_input));

@@ -107,6 +107,7 @@ _SIGNATURES = {
     "gemm_tc": {
         "zai_gemm_tc_supports": [_I, _I, _I, _I],
         "zai_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
+        "zai_gemm_tc_grouped": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     },
     "gemm_tc_pair": {
         "zai_gemm_pair_supports": [_I, _I, _I, _I],
@@ -1394,6 +1395,8 @@ def rmsnorm_rows(x, w, eps):
     return out
 
 
+USE_MOE_GROUPED_TC = os.environ.get("ZAI_MOE_GROUPED_TC", "1") == "1"
+MOE_GROUPED_TILE_ROWS = 64   # from this many rows per expert on average, tiles of 128 rows on the tcgen05 kernel (bfloat16)
 MOE_TALL_TILE_ROWS = 32      # from this many rows per expert on average, tiles of 64 rows instead of 16 (bfloat16)
 
 
@@ -1417,7 +1420,11 @@ def routed_experts(x, w_router, w_gate_up, w_down, top, renorm=False, weight_on=
     if N == 0:
         return out
     tall = dt == _BF16 and W % 8 == 0 and F % 8 == 0 and N * top >= MOE_TALL_TILE_ROWS * E
-    TM = 64 if tall else 16
+    # many rows an expert: tiles of 128 rows and both products on the 5th-generation tensor cores (grouped tcgen05)
+    grouped = (tall and USE_MOE_GROUPED_TC and N * top >= MOE_GROUPED_TILE_ROWS * E
+               and _fn("gemm_tc", "zai_gemm_tc_supports")(128, 2 * F, W, _EPI_SWIGLU)
+               and _fn("gemm_tc", "zai_gemm_tc_supports")(128, W, F, _EPI_F32))
+    TM = 128 if grouped else 64 if tall else 16
     max_tiles = _fn(lib, "zai_moe_max_tiles")(N, top, E, TM)
     if max_tiles < 0:
         raise KernelError("routed_experts: too many rows")
@@ -1433,9 +1440,18 @@ def routed_experts(x, w_router, w_gate_up, w_down, top, renorm=False, weight_on=
     _check(_fn(lib, "zai_moe_gather")(_ptr(x_sorted), _ptr(dest), _ptr(tile_expert), xp, xs, dt, _ptr(ids), _ptr(wts), _ptr(rank),
                                       _ptr(counts), N, W, E, top, TM, max_tiles, on_input, _stream()), "moe_gather")
     act = torch.empty((rows, F), dtype=x.dtype, device=dev)
+    y = torch.empty((rows, W), dtype=torch.float32, device=dev)
+    if grouped:
+        tc = _fn("gemm_tc", "zai_gemm_tc_grouped")
+        _check(tc(_ptr(act), _ptr(w_gate_up), _ptr(x_sorted), _ptr(tile_expert), _status_ptr(dev), max_tiles, E, 2 * F, W,
+                  _EPI_SWIGLU, _stream()), "gemm_tc_grouped (gate/up)")
+        _check(tc(_ptr(y), _ptr(w_down), _ptr(act), _ptr(tile_expert), _status_ptr(dev), max_tiles, E, W, F, _EPI_F32, _stream()),
+               "gemm_tc_grouped (down)")
+        _check(_fn(lib, "zai_moe_combine")(_ptr(out), dt, _ptr(y), _ptr(dest), _ptr(wts), N, W, top, 1 - on_input, _stream()),
+               "moe_combine")
+        return out
     _check(_fn(lib, "zai_moe_gemm")(_ptr(act), int(dt == _F32), _ptr(x_sorted), _ptr(w_gate_up), dt, _ptr(tile_expert), max_tiles,
                                     TM, W, F, 1, _stream()), "moe_gemm (gate/up)")
-    y = torch.empty((rows, W), dtype=torch.float32, device=dev)
     _check(_fn(lib, "zai_moe_gemm")(_ptr(y), 1, _ptr(act), _ptr(w_down), dt, _ptr(tile_expert), max_tiles, TM, F, W, 0, _stream()),
            "moe_gemm (down)")
     _check(_fn(lib, "zai_moe_combine")(_ptr(out), dt, _ptr(y), _ptr(dest), _ptr(wts), N, W, top, 1 - on_input, _stream()),

@@ -106,7 +106,7 @@ class RoutedExperts(FeedForward):
     `{e}` standing for the expert's number."""
     accepts_lazy_input = False    # the router and the experts read the normed rows themselves
     graph_safe = True             # routing stays on the device: forward launches kernels only
-    kernel_libs = ("moe",)
+    kernel_libs = ("moe", "gemm_tc")      # (gemm_tc: the grouped products of steps with many rows an expert, bfloat16)
 
     def __init__(self, hidden: int, ff_dim: int, experts: int, top: int, renormalize: bool = False, weight_on: str = "input",
                  names=None):
