@@ -36,7 +36,8 @@
 #define TC_THREADS 192
 #define TC_SPIN_LIMIT 4000000
 
-enum { TC_EPI_BF16 = 0, TC_EPI_F32 = 1, TC_EPI_SWIGLU = 2 };
+enum { TC_EPI_BF16 = 0, TC_EPI_F32 = 1, TC_EPI_SWIGLU = 2,
+       TC_EPI_F32_PAIR = 3 };   // (grouped products only) 32-bit results, two adjacent weight tiles against one token tile
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -106,7 +107,8 @@ __device__ __forceinline__ int tc_group_of(const TcArgs& a, int t) { return a.ti
 template <int BN, int EPI, int ACC_BUFS>
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                              const __grid_constant__ CUtensorMap map_x, const TcArgs a) {
-    constexpr int NA = EPI == TC_EPI_SWIGLU ? 2 : 1;           // accumulators per tile (weight tiles per stage)
+    constexpr int NA = (EPI == TC_EPI_SWIGLU || EPI == TC_EPI_F32_PAIR) ? 2 : 1;   // accumulators per tile (weight tiles per stage)
+    constexpr int OT = EPI == TC_EPI_F32_PAIR ? 2 * TC_BM : TC_BM;                 // rows of W (columns of y) per tile
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
     constexpr uint32_t STAGE_BYTES = NA * A_BYTES + B_BYTES;
     constexpr uint32_t TILE_COLS = NA * BN;                    // TMEM columns of one tile's accumulators
@@ -153,7 +155,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
             for (int t = blockIdx.x; t < a.tiles && ok; t += gridDim.x) {
                 const int grp = tc_group_of(a, t);
                 if (grp < 0) continue;
-                const int o0 = (t % a.tiles_o) * TC_BM, n0 = (t / a.tiles_o) * BN;
+                const int o0 = (t % a.tiles_o) * OT, n0 = (t / a.tiles_o) * BN;
                 const int w0 = grp * a.group_rows + o0;        // (a tile that runs past its matrix reads rows that the epilogue drops)
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % stages;
@@ -162,7 +164,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                     unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
                     mbar_expect_tx(&full_bar[s], STAGE_BYTES);
                     tma_load_2d(st, &map_w, kb * TC_BK, w0, &full_bar[s]);
-                    if (NA == 2) tma_load_2d(st + A_BYTES, &map_w, kb * TC_BK, a.F + w0, &full_bar[s]);
+                    if (NA == 2) tma_load_2d(st + A_BYTES, &map_w, kb * TC_BK, (EPI == TC_EPI_SWIGLU ? a.F : TC_BM) + w0, &full_bar[s]);
                     tma_load_2d(st + NA * A_BYTES, &map_x, kb * TC_BK, n0, &full_bar[s]);
                     issued = it + 1;
                 }
@@ -224,7 +226,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
             if (tc_group_of(a, t) < 0) continue;
             ++local;
             const int buf = local % ACC_BUFS;
-            const int o = (t % a.tiles_o) * TC_BM + row, n0 = (t / a.tiles_o) * BN;
+            const int o = (t % a.tiles_o) * OT + row, n0 = (t / a.tiles_o) * BN;
             if (!mbar_wait(&acc_full_bar[buf], (local / ACC_BUFS) & 1, failed) || *failed) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t acc = tmem_base + buf * TILE_COLS + ((uint32_t)(q * 32) << 16);
@@ -232,7 +234,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32], u[32];
                 tmem_ld32(acc + c0, r);
-                if (EPI == TC_EPI_SWIGLU) tmem_ld32(acc + BN + c0, u);
+                if (NA == 2) tmem_ld32(acc + BN + c0, u);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (c0 + 32 >= BN) {                           // everything of this buffer is in registers now
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -248,6 +250,9 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                             const float up = __uint_as_float(u[j]);
                             reinterpret_cast<bf16*>(a.y)[(size_t)n * a.ldy + o] =
                                 __float2bfloat16_rn(__fdividef(v, 1.f + __expf(-v)) * up);
+                        } else if (EPI == TC_EPI_F32_PAIR) {
+                            reinterpret_cast<float*>(a.y)[(size_t)n * a.ldy + o] = v;
+                            if (o + TC_BM < o_limit) reinterpret_cast<float*>(a.y)[(size_t)n * a.ldy + o + TC_BM] = __uint_as_float(u[j]);
                         } else if (EPI == TC_EPI_F32) {
                             reinterpret_cast<float*>(a.y)[(size_t)n * a.ldy + o] = v;
                         } else {
@@ -310,7 +315,7 @@ static int sm_count() {
 
 template <int BN, int EPI, int ACC_BUFS>
 static int tc_launch(const CUtensorMap& mw, const CUtensorMap& mx, TcArgs a, int o_tiles, cudaStream_t stream) {
-    constexpr int NA = EPI == TC_EPI_SWIGLU ? 2 : 1;
+    constexpr int NA = (EPI == TC_EPI_SWIGLU || EPI == TC_EPI_F32_PAIR) ? 2 : 1;
     const size_t stage = (size_t)NA * TC_BM * TC_BK * 2 + (size_t)BN * TC_BK * 2;
     int stages = (int)(((size_t)200 * 1024) / stage);
     if (stages > 8) stages = 8;
@@ -375,8 +380,10 @@ ZAI_API int zai_gemm_tc_grouped(void* y, const void* W, const void* x, const int
                                 int O, int K, int epilogue, cudaStream_t stream) {
     if (n_tiles <= 0) return ZAI_OK;
     const long long rows = (long long)n_tiles * 128, w_rows = (long long)groups * O;
-    if (groups < 1 || rows > 0x7fffffff || w_rows > 0x7fffffff || !zai_gemm_tc_supports((int)rows, O, K, epilogue)) return ZAI_BAD_SIZE;
+    const bool pair = epilogue == TC_EPI_F32_PAIR;
+    if (pair) epilogue = TC_EPI_F32;
     if (epilogue != TC_EPI_BF16 && epilogue != TC_EPI_F32 && epilogue != TC_EPI_SWIGLU) return ZAI_BAD_SIZE;
+    if (groups < 1 || rows > 0x7fffffff || w_rows > 0x7fffffff || !zai_gemm_tc_supports((int)rows, O, K, epilogue)) return ZAI_BAD_SIZE;
     if ((reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(x) & 15) || !tile_group) return ZAI_BAD_SIZE;
     CUtensorMap mw, mx;
     int e = make_map(&mw, W, (int)w_rows, K, TC_BM);
@@ -391,6 +398,9 @@ ZAI_API int zai_gemm_tc_grouped(void* y, const void* W, const void* x, const int
     a.tile_group = tile_group; a.group_rows = O;
     const int o_tiles = ((epilogue == TC_EPI_SWIGLU ? a.F : O) + TC_BM - 1) / TC_BM;
     if (epilogue == TC_EPI_BF16) return tc_launch<128, TC_EPI_BF16, 2>(mw, mx, a, o_tiles, stream);
+    // two weight tiles a stage share the token tile (half the token tiles' traffic from L2 per product, as in the
+    // gate/up product)
+    if (pair && O > TC_BM) return tc_launch<128, TC_EPI_F32_PAIR, 2>(mw, mx, a, (O + 2 * TC_BM - 1) / (2 * TC_BM), stream);
     if (epilogue == TC_EPI_F32) return tc_launch<128, TC_EPI_F32, 2>(mw, mx, a, o_tiles, stream);
     return tc_launch<128, TC_EPI_SWIGLU, 2>(mw, mx, a, o_tiles, stream);
 }

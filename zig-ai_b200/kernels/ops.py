@@ -165,9 +165,11 @@ def _check(code: int, what: str, n: int = 1) -> None:
     raise KernelError(f"{what}: CUDA error {code} at launch")
 
 
-CORE_LIBS = ("embed", "norm", "activation", "rope_kv", "attention")
-BF16_LIBS = ("attention_mma", "attention_tma", "attention_tc", "decode_gemm")
-BF16_ONLY = ("gemm_tc", "gemm_tc_pair", "stream_gemm")       # libraries that a part may name and only a bfloat16 model uses
+CORE_LIBS = ("embed", "norm", "activation", "rope_kv")
+BF16_LIBS = ("decode_gemm",)
+# libraries that a part may name and only a bfloat16 model uses
+BF16_ONLY = ("gemm_tc", "gemm_tc_pair", "stream_gemm", "attention_mma", "attention_tma", "attention_tc")
+ATTENTION_LIBS = ("attention", "attention_mma", "attention_tma", "attention_tc")
 
 
 def require(dtype=None, extra=()) -> None:
@@ -180,7 +182,7 @@ def require(dtype=None, extra=()) -> None:
     bf16 = dtype is None or dtype == torch.bfloat16
     libs = list(CORE_LIBS) + [x for x in extra if x not in CORE_LIBS and (bf16 or x not in BF16_ONLY)]
     if dtype is None:
-        libs += ["shortconv", "sampling"]
+        libs += ["shortconv", "sampling", *ATTENTION_LIBS]
     if bf16:
         libs += list(BF16_LIBS)
         if dtype is None or USE_TC_GEMM:
@@ -348,6 +350,7 @@ fuses_norm = True       # `linear` and `linear_swiglu` take a LazyNorm and apply
 fuses_layernorm = True  # ... also one that is a layer norm (`LazyNorm.beta`)
 
 _EPI_BF16, _EPI_F32, _EPI_SWIGLU = 0, 1, 2
+_EPI_F32_PAIR = 3          # (grouped tcgen05 products) 32-bit results, two weight tiles a stage
 
 
 @_timed("embedding")
@@ -1396,6 +1399,7 @@ def rmsnorm_rows(x, w, eps):
 
 
 USE_MOE_GROUPED_TC = os.environ.get("ZAI_MOE_GROUPED_TC", "1") == "1"
+USE_MOE_DOWN_PAIR = os.environ.get("ZAI_MOE_DOWN_PAIR", "1") == "1"      # the down product: two weight tiles a stage
 MOE_GROUPED_TILE_ROWS = 64   # from this many rows per expert on average, tiles of 128 rows on the tcgen05 kernel (bfloat16)
 MOE_TALL_TILE_ROWS = 32      # from this many rows per expert on average, tiles of 64 rows instead of 16 (bfloat16)
 
@@ -1445,7 +1449,8 @@ def routed_experts(x, w_router, w_gate_up, w_down, top, renorm=False, weight_on=
         tc = _fn("gemm_tc", "zai_gemm_tc_grouped")
         _check(tc(_ptr(act), _ptr(w_gate_up), _ptr(x_sorted), _ptr(tile_expert), _status_ptr(dev), max_tiles, E, 2 * F, W,
                   _EPI_SWIGLU, _stream()), "gemm_tc_grouped (gate/up)")
-        _check(tc(_ptr(y), _ptr(w_down), _ptr(act), _ptr(tile_expert), _status_ptr(dev), max_tiles, E, W, F, _EPI_F32, _stream()),
+        _check(tc(_ptr(y), _ptr(w_down), _ptr(act), _ptr(tile_expert), _status_ptr(dev), max_tiles, E, W, F,
+                  _EPI_F32_PAIR if USE_MOE_DOWN_PAIR else _EPI_F32, _stream()),
                "gemm_tc_grouped (down)")
         _check(_fn(lib, "zai_moe_combine")(_ptr(out), dt, _ptr(y), _ptr(dest), _ptr(wts), N, W, top, 1 - on_input, _stream()),
                "moe_combine")

@@ -40,6 +40,7 @@ from .base import Mixer, PagedKVNeed, ParamDecl, make_part, register_part, PartS
 class Attention(Mixer):
     accepts_lazy_input = True     # x goes straight into a product
     graph_safe = True      # forward launches kernels only; nothing is read back to the host
+    kernel_libs = ("attention", "attention_mma", "attention_tma", "attention_tc")   # (all but the first: bfloat16 only)
 
     def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, qk_norm: bool, eps: float,
                  position: PartSpec, window=None, scale=None, kv_proj: bool = True, value_dim=None,
@@ -73,7 +74,7 @@ class Attention(Mixer):
         if self.prepared and (self.value_norm or not self.kv_proj):
             raise ValueError("value_norm and a borrowed cache are not combined with bias, whole norm, chunk or gate")
         if self.prepared:
-            self.kernel_libs = ("qkv_prepare",)
+            self.kernel_libs = type(self).kernel_libs + ("qkv_prepare",)
 
     def params(self):
         q_dim, kv_dim = self.heads * self.head_dim, self.kv_heads * self.head_dim
