@@ -13,6 +13,7 @@
 //     its D rows in registers; the operands of the next sixteen tokens come into shared memory by
 //     asynchronous copies while the current sixteen are computed;
 //   * the output norm: o / rms(o) * weight * silu(gate) per head, rounded to the model's dtype.
+#include <cstdlib>
 #include "common.cuh"
 
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
@@ -346,16 +347,49 @@ ZAI_API int zai_delta_prepare(float* qk_out, float* bg_out, float* gch_out, cons
         (const T*)qkv, qkv_stride, (const T*)b_in, b_stride, (const T*)a_in, a_stride, a_log, dt_bias, H, G, D, unit_eps));
 }
 
+// Dynamic shared memory that keeps more than `per_sm` blocks of `kernel` off one SM.  The recurrence is a chain of
+// dependent instructions per warp, so a block runs fastest with an SM's schedulers to itself; but a grid that is
+// launched while the kernel before it still drains (as dependent launches are) is placed on the first SMs that have
+// room, several blocks to an SM with other SMs left empty (measured: 64 blocks after a large kernel, 1130 us instead
+// of 640).  Unused shared memory makes the placement even whatever runs before.
+template <typename K>
+static size_t delta_spread_smem(K kernel, long long blocks) {
+    static int sms = 0, sm_smem = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        cudaDeviceGetAttribute(&sm_smem, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev);
+        if (sms < 1) sms = 1;
+    }
+    const long long per_sm = (blocks + sms - 1) / sms;
+    if (per_sm >= 4) return 0;
+    cudaFuncAttributes fa;
+    if (cudaFuncGetAttributes(&fa, kernel) != cudaSuccess) return 0;
+    // every block takes its static and dynamic bytes and 1 KB of the system's: per_sm blocks fit, per_sm + 1 do not
+    const long long each = sm_smem / per_sm - 1024 - (long long)fa.sharedSizeBytes - 1024;
+    const long long next = sm_smem / (per_sm + 1) - 1024 - (long long)fa.sharedSizeBytes;
+    if (each <= 0 || each <= next) return 0;
+    const long long dyn = each > 160 * 1024 ? 160 * 1024 : each;
+    if (dyn <= next || dyn <= 0) return 0;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return (size_t)dyn;
+}
+
 template <typename T, int DP, int P>
 static int launch_delta(float* o_out, const float* qk, const float* bg, const float* gch, const void* v_in, int v_stride,
                         float* state, const int* cu_q, const int* slot_ids, int n_seqs, int H, int G, int D, int V, int write_state,
                         int num_slots, int* status, cudaStream_t stream) {
     const int vb = 128 / P;
+    const dim3 grid(n_seqs, H, (V + vb - 1) / vb);
+    const long long blocks = (long long)grid.x * grid.y * grid.z;
     if (gch)
-        return launch_pdl(gated_delta_kernel<T, DP, P, true>, dim3(n_seqs, H, (V + vb - 1) / vb), dim3(128), 0, stream, o_out, qk, bg,
-                          gch, (const T*)v_in, v_stride, state, cu_q, slot_ids, H, G, D, V, write_state, num_slots, status);
-    return launch_pdl(gated_delta_kernel<T, DP, P, false>, dim3(n_seqs, H, (V + vb - 1) / vb), dim3(128), 0, stream, o_out, qk, bg,
-                      gch, (const T*)v_in, v_stride, state, cu_q, slot_ids, H, G, D, V, write_state, num_slots, status);
+        return launch_pdl(gated_delta_kernel<T, DP, P, true>, grid, dim3(128), delta_spread_smem(gated_delta_kernel<T, DP, P, true>, blocks),
+                          stream, o_out, qk, bg, gch, (const T*)v_in, v_stride, state, cu_q, slot_ids, H, G, D, V, write_state, num_slots,
+                          status);
+    return launch_pdl(gated_delta_kernel<T, DP, P, false>, grid, dim3(128), delta_spread_smem(gated_delta_kernel<T, DP, P, false>, blocks),
+                      stream, o_out, qk, bg, gch, (const T*)v_in, v_stride, state, cu_q, slot_ids, H, G, D, V, write_state, num_slots,
+                      status);
 }
 
 // o_out [N, H*V] 32-bit; qk, bg (and gch, or null) from zai_delta_prepare; v_in [N, v_stride] (heads of V values);
