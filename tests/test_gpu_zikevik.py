@@ -13,7 +13,7 @@ import torch
 import plain_zikevik as P
 import traces
 from test_zikevik_cpu import random_configuration, tokens, with_tensors
-from zikevik_configs import ALL, ONLY, PAGE_SIZE
+from zikevik_configs import ALL, ONLY, PAGE_SIZE, medium_configuration, odd_configuration
 from zig_ai_b200.config import config_from_dict
 from zig_ai_b200.weights import write_random_model
 
@@ -221,6 +221,31 @@ def test_random_configurations(tmp_path, seed):
     got = run_cuts(r, toks, {"w": [150], "p": [9, 2, 17, 1, 1, 3, 30, 2, 5] * 2 + [10], "d": [110] + [1] * 40})
     for rid, rows in got.items():
         traces.check_request(rows, want, "float32", f"random configuration {seed}, cut {rid}")
+
+
+@pytest.mark.parametrize("kind,seed", [("medium", s) for s in range(5)] + [("odd", s) for s in range(5)])
+def test_medium_and_odd_configurations(tmp_path, kind, seed):
+    """Configurations drawn at random at sizes that the tensor-core kernels take, and at sizes that are no multiple of
+    eight anywhere, in both modes: whole, in portions and with a decoded tail.  32-bit: every row.  bfloat16 (routers
+    with close calls among them): the median row."""
+    from zig_ai_b200.engine.runner import load_runner
+    g = random.Random(9100 + seed)
+    cfg = (medium_configuration if kind == "medium" else odd_configuration)(g)
+    d = str(tmp_path / "m")
+    write_random_model(config_from_dict(cfg), seed, d, matrix_std="fan_in")
+    c, W = P.read_config(d), P.read_weights(d)
+    T = 260
+    toks = tokens(cfg["vocab"], T, seed)
+    want = P.forward(c, W, toks).numpy()
+    cuts = {"w": [T], "p": [7, 2, 33, 1, 64, 3, 100, 19, 2, 29], "d": [T - 30] + [1] * 30}
+    for dtype in ("float32", "bfloat16"):
+        r = load_runner(d, dtype, max_tokens=384, max_requests=4, page_size=g.choice([16, 64]))
+        for rid, rows in run_cuts(r, toks, cuts).items():
+            if dtype == "float32":
+                traces.check_request(rows, want, dtype, f"{kind} configuration {seed}, cut {rid}")
+            else:
+                e = traces.request_errors(rows, want)
+                assert np.median(e) < 0.12, f"{kind} configuration {seed}, bfloat16, cut {rid}: half of the rows are off by more than {np.median(e):.3f}"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -88,3 +88,53 @@ Z_C = config(1000, 320, 1e-6, 0.8, _with_repeats([
 
 ALL = {"A": (Z_A, 31), "B": (Z_B, 37), "C": (Z_C, 41)}
 PAGE_SIZE = {"A": 8, "B": 16, "C": 64}
+
+
+# ----------------------------------------------------------------------------- configurations drawn at random
+import copy  # noqa: E402
+
+
+def odd_configuration(g):
+    """Sizes that are no multiple of eight anywhere: widths, heads, head sizes, ranks, inner sizes, experts."""
+    layers = []
+    for i in range(g.randint(2, 5)):
+        own = [j for j, l in enumerate(layers) if "weights_of" not in l]
+        if own and g.random() < 0.2:
+            j = g.choice(own); layers.append(dict(copy.deepcopy(layers[j]), weights_of=j)); continue
+        r = g.random()
+        if r < 0.1: mlp = None
+        elif r < 0.45: mlp = dense(g.choice([100, 130, 257, 300]))
+        else:
+            E = g.choice([1, 3, 5, 7, 12]); mlp = moe(g.choice([20, 52, 100, 132]), E, g.choice([1, min(2, E), E]))
+        if g.random() < 0.45:
+            heads = g.choice([1, 2, 3, 5, 6]); kv = g.choice([k for k in (1, 2, 3, 5, 6) if heads % k == 0])
+            layers.append(delta(heads, kv, g.choice([12, 20, 24, 40, 72]), g.choice([12, 20, 36, 40, 100]), g.choice([1, 2, 3, 5, 7]),
+                                g.choice([3, 5, 12, 20]), g.choice([3, 7, 12, 36]), mlp=mlp))
+        else:
+            layers.append(latent(g.choice([1, 3, 5, 7, 9, 17]), g.choice([4, 12, 20, 24, 40]), g.choice([2, 6, 12, 20, 24]), g.choice([12, 20, 36, 100]),
+                                 g.choice([20, 40, 72, 100, 132]), g.choice([20, 36, 72, 100]), g.choice([0.1, 0.2]),
+                                 g.choice([10000.0, 1e6]), mlp=mlp))
+    return config(g.choice([101, 449, 1001]), g.choice([50, 100, 132, 250, 98]), g.choice([1e-5, 1e-6]), g.choice([0.5, 1.0]), layers)
+
+
+def medium_configuration(g):
+    """Sizes between the tiny test models and a real model's layers, which the tensor-core kernels take in bfloat16."""
+    layers = []
+    for i in range(g.randint(3, 7)):
+        own = [j for j, l in enumerate(layers) if "weights_of" not in l]
+        if own and g.random() < 0.2:
+            j = g.choice(own); layers.append(dict(copy.deepcopy(layers[j]), weights_of=j)); continue
+        r = g.random()
+        if r < 0.1: mlp = None
+        elif r < 0.45: mlp = dense(g.choice([96, 200, 320, 512, 768]))
+        else:
+            E = g.choice([2, 4, 6, 8, 16]); mlp = moe(g.choice([48, 64, 96, 136, 256]), E, g.choice([1, 2, min(4, E)]))
+        if g.random() < 0.45:
+            heads = g.choice([1, 2, 3, 4, 6, 8]); kv = g.choice([k for k in (1, 2, 3, 4, 6, 8) if heads % k == 0])
+            layers.append(delta(heads, kv, g.choice([16, 32, 48, 64, 128]), g.choice([16, 32, 64, 96, 128]), g.choice([2, 3, 4, 5]),
+                                g.choice([8, 16, 24, 40]), g.choice([8, 16, 32, 48]), mlp=mlp))
+        else:
+            layers.append(latent(g.choice([2, 3, 4, 6, 8, 16]), g.choice([16, 32, 48, 64]), g.choice([8, 16, 32, 64]), g.choice([16, 32, 48, 64, 128]),
+                                 g.choice([32, 48, 64, 96, 128, 256]), g.choice([48, 64, 96, 128, 192]), g.choice([0.08, 0.125, 0.2]),
+                                 g.choice([10000.0, 20000.0, 5e5]), mlp=mlp))
+    return config(g.choice([257, 500, 1000, 2048]), g.choice([96, 128, 160, 200, 256, 320, 384]), g.choice([1e-5, 1e-6]), g.choice([0.5, 1.0, 2.0]), layers)
