@@ -190,7 +190,8 @@ def kv_write(k, v, step, cache, kv_heads, head_dim):
     cache.pages[page, 1, :, off, :] = v.reshape(N, kv_heads, head_dim).to(cache.pages.dtype)
 
 
-def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=None, chunk=None):
+def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=None, chunk=None, softcap=None, bias=None, sink=None,
+                    keep_first=0, impl=None):
     N = q.shape[0]
     D, ps = head_dim, cache.page_size
     out = torch.empty((N, heads * D), dtype=q.dtype, device=q.device)
@@ -214,15 +215,30 @@ def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=Non
         qpos = torch.arange(ctx[s], total, device=q.device)[:, None]
         kpos = torch.arange(total, device=q.device)[None, :]
         mask = kpos > qpos
+        if softcap:
+            sc = softcap * torch.tanh(sc / softcap)
+        if bias is not None:                 # by distance, the table's last row for everything beyond it
+            dist = torch.clamp(qpos - kpos, min=0, max=bias.shape[0] - 1)
+            sc = sc + _f(bias)[dist].permute(2, 0, 1)
         if window is not None:
-            mask = mask | (kpos <= qpos - window)
+            mask = mask | ((kpos <= qpos - window) & (kpos >= int(keep_first or 0)))
         if chunk is not None:
             mask = mask | (kpos < qpos - qpos % chunk)
         sc = sc.masked_fill(mask[None], float("-inf"))
-        p = torch.softmax(sc, dim=-1)
+        if sink is not None:                 # one more term of the denominator, with no value
+            sc = torch.cat([sc, _f(sink)[:, None, None].expand(heads, b - a, 1)], dim=-1)
+            p = torch.softmax(sc, dim=-1)[..., :-1]
+        else:
+            p = torch.softmax(sc, dim=-1)
         o = torch.einsum("hnk,hkd->hnd", p, v).permute(1, 0, 2).reshape(b - a, heads * D)
         out[a:b] = o.to(q.dtype)
     return out
+
+
+def add_cast(h, delta, out_dtype, delta_gamma=None, delta_eps=0.0):
+    if delta is not None:
+        h += _f(delta) if delta_gamma is None else _normed(delta, delta_gamma, delta_eps)
+    return h.to(out_dtype) if out_dtype != h.dtype else h.clone()
 
 
 def gather_add(h, pending, rows, pending_gamma=None, pending_eps=0.0):
@@ -441,6 +457,19 @@ def stretched_frequencies(rotary_dim, theta, scaling):
     f = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -2.0 * i / rotary_dim)
     if scaling is None:
         return f, 1.0
+    if scaling[0] == "wavelength":          # stretched by wavelength: (tag, factor, low, high, original)
+        _, factor, low, high, original = scaling
+        out = []
+        for fi in f.tolist():
+            wave = 2.0 * math.pi / fi
+            if wave < original / high:
+                out.append(fi)
+            elif wave > original / low:
+                out.append(fi / factor)
+            else:
+                smooth = (original / wave - low) / (high - low)
+                out.append((1.0 - smooth) * fi / factor + smooth * fi)
+        return torch.tensor(out, dtype=torch.float64), 1.0
     factor, original, fast, slow = scaling
     where = lambda turns: rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
     lo, hi = max(math.floor(where(fast)), 0), min(math.ceil(where(slow)), rotary_dim - 1)
@@ -459,7 +488,8 @@ def rope_table(step, rotary_dim, theta, device, scaling=None):
     return t
 
 
-def qkv_prepare(y, q_w, k_w, eps, scope, table, rot, step, cache, heads, kv_heads, dim, vdim, cache_dim, write=True):
+def qkv_prepare(y, q_w, k_w, eps, scope, table, rot, step, cache, heads, kv_heads, dim, vdim, cache_dim, write=True, temp=None,
+                v_first=None, v_lambda=None):
     """From projection rows y = [q (H D) | k (G D) | v (G Dv) | ...]: RMS norm of q and k (scope 0 none, 1 per head,
     2 over the whole projection), rotation of pairs (i, i + rot/2) from the table, k and v into the pages (heads
     `cache_dim` wide, zeros behind their own values); returns q [N, H * cache_dim]."""
@@ -472,6 +502,11 @@ def qkv_prepare(y, q_w, k_w, eps, scope, table, rot, step, cache, heads, kv_head
     if scope == 1:
         q, k = _rms(q, q_w, eps), _rms(k, k_w, eps)
     q, k = _rotate(q, step.positions, rot, 1.0, table), _rotate(k, step.positions, rot, 1.0, table)
+    if temp:                                 # the queries' temperature, a step function of the position
+        coef, every = temp
+        q = q * (1.0 + coef * torch.log((torch.div(step.positions + 1, every, rounding_mode="floor") + 1).float()))[:, None, None]
+    if v_first is not None:                  # values mixed with an earlier layer's values of the same rows
+        v = ((1.0 - _f(v_lambda)) * _f(v) + _f(v_lambda) * _f(v_first)).to(y.dtype)
     pad = lambda t, n: torch.cat([t, t.new_zeros(t.shape[:-1] + (n - t.shape[-1],))], dim=-1)
     if write:
         page, off = _page_rows(step, cache)
@@ -559,22 +594,65 @@ def rmsnorm_rows(x, w, eps):
     return (y if w is None else y * w).to(x.dtype)
 
 
-def routed_experts(x, w_router, w_gate_up, w_down, top, renorm=False, weight_on="input"):
+def routed_experts(x, w_router, w_gate_up, w_down, top, renorm=False, weight_on="input", score="sigmoid", act="silu", limit=0.0,
+                   alpha=1.702):
     """Every row to the `top` experts with the largest sigmoid(x . w_router^T); the scores weigh the experts' inputs
     or outputs; w_gate_up [E, 2F, W] (gate rows, then up rows), w_down [E, W, F]."""
     N, W = x.shape
     E, F = w_gate_up.shape[0], w_gate_up.shape[1] // 2
-    s = torch.sigmoid(_f(x) @ _f(w_router).t())
+    z = _f(x) @ _f(w_router).t()
+    s = torch.softmax(z, dim=-1) if score == "softmax" else torch.sigmoid(z)
     val, idx = torch.topk(s, int(top), dim=-1)
     if renorm:
-        val = val / val.sum(-1, keepdim=True)
+        val = val / (val.sum(-1, keepdim=True) + 1e-20)
     out = torch.zeros((N, W), dtype=torch.float32, device=x.device)
     for n in range(N):
         for k in range(int(top)):
             e, w = int(idx[n, k]), val[n, k]
             xin = (_f(x[n]) * w).to(x.dtype) if weight_on == "input" else x[n]
             gu = _f(xin) @ _f(w_gate_up[e]).t()
-            act = (_silu(gu[:F]) * gu[F:]).to(x.dtype)
-            y = _f(act) @ _f(w_down[e]).t()
+            if act == "clamped":
+                g, u = torch.clamp(gu[:F], max=limit), torch.clamp(gu[F:], min=-limit, max=limit)
+                hid = (g * torch.sigmoid(alpha * g) * (u + 1.0)).to(x.dtype)
+            else:
+                hid = (_silu(gu[:F]) * gu[F:]).to(x.dtype)
+            y = _f(hid) @ _f(w_down[e]).t()
             out[n] += y if weight_on == "input" else y * w
     return out.to(x.dtype)
+
+
+def act_mul(gu, ff_dim, kind):
+    return (_f(activation(_f(gu[:, :ff_dim]), kind)) * _f(gu[:, ff_dim:2 * ff_dim])).to(gu.dtype)
+
+
+def linear_glu(x, w_gate_up, ff_dim, kind):
+    return act_mul(linear(x, w_gate_up), ff_dim, kind)
+
+
+def mlstm(y, at, bias_i, bias_f, cap, norm_w, eps, state, step, heads, dim, vdim, write_state=True):
+    """The matrix memory with log gates over the stacked projections y (columns `at`: q, k, v, output gate, the two log
+    gates' inputs); state [slots, H, D + 1, Dv + 1]: S with the normaliser as its last column, the running maximum of
+    every column in the last row."""
+    N, H, D, Dv = y.shape[0], heads, dim, vdim
+    q_at, k_at, v_at, g_at, i_at, f_at = at
+    q = _f(y[:, q_at:q_at + H * D]).reshape(N, H, D) * D ** -0.5
+    k = _f(y[:, k_at:k_at + H * D]).reshape(N, H, D)
+    v = torch.cat([_f(y[:, v_at:v_at + H * Dv]).reshape(N, H, Dv), torch.ones(N, H, 1)], dim=-1)
+    gi = cap * torch.tanh((_f(y[:, i_at:i_at + H]) + bias_i) / cap)
+    gf = torch.nn.functional.logsigmoid(cap * torch.tanh((_f(y[:, f_at:f_at + H]) + bias_f) / cap))
+    out = torch.zeros((N, H, Dv), dtype=torch.float32)
+    for a, b, slot in _spans(step, state):
+        S, m = state[slot][:, :D, :].clone(), state[slot][:, D, 0].clone()
+        for t in range(a, b):
+            new = torch.maximum(gf[t] + m, gi[t])
+            keep, take = torch.exp(gf[t] + m - new), torch.exp(gi[t] - new)
+            S = keep[:, None, None] * S + take[:, None, None] * k[t][:, :, None] * v[t][:, None, :]
+            m = new
+            r = torch.einsum("hdc,hd->hc", S, q[t])
+            out[t] = r[:, :Dv] / (torch.maximum(r[:, Dv].abs(), torch.exp(-m)) + 1e-6)[:, None]
+        if write_state:
+            state[slot][:, :D, :] = S
+            state[slot][:, D, :] = m[:, None]
+    o = out * torch.rsqrt((out * out).mean(-1, keepdim=True) + eps)
+    g = torch.sigmoid(_f(y[:, g_at:g_at + H * Dv]))
+    return (o.reshape(N, H * Dv) * norm_w * g).to(y.dtype)

@@ -13,7 +13,8 @@ The reference gives every attention layer a block table of its own drawing from 
   request's slot.
 * pages are taken just before the step that fills them, given back when the request ends, and,
   in a window group, as soon as every position of the page has left the window (in a group whose
-  layers see back to the start of a chunk of positions: as soon as the page lies before the chunk).
+  layers see back to the start of a chunk of positions: as soon as the page lies before the chunk);
+  a window group that keeps the request's first positions visible never gives their pages back.
 * page 0 of every paged group and slot 0 are never handed out: padding rows of a fixed-shape
   decode batch point at them.
 """
@@ -140,6 +141,11 @@ class CacheManager:
         first_pos = max(cached - grp.need.window + 1, 0)
         return first_pos // self.page_size
 
+    def _kept_pages(self, grp: CacheGroup) -> int:
+        """Logical pages at the front that a window never gives back: those that hold the request's kept first positions."""
+        keep = getattr(grp.need, "keep_first", 0) or 0
+        return -(-int(keep) // self.page_size)
+
     def pages_to_take(self, request_id, total_tokens: int) -> Dict[int, int]:
         """Pages each paged group would have to hand out so that the request can hold positions
         0..total_tokens-1 (counting what `reserve` would first give back)."""
@@ -149,7 +155,7 @@ class CacheManager:
         for gi in self.paged_groups():
             grp, table = self.groups[gi], rc.tables[gi]
             first = self._first_needed_page(grp, rc.num_tokens)
-            gives_back = sum(1 for j in range(min(first, len(table))) if table[j] != RELEASED)
+            gives_back = sum(1 for j in range(self._kept_pages(grp), min(first, len(table))) if table[j] != RELEASED)
             takes = max(n_logical - max(len(table), first), 0)
             out[gi] = takes - gives_back
         return out
@@ -221,7 +227,7 @@ class CacheManager:
         for gi in self.paged_groups():
             grp, table = self.groups[gi], rc.tables[gi]
             first = self._first_needed_page(grp, rc.num_tokens)
-            for j in range(min(first, len(table))):
+            for j in range(self._kept_pages(grp), min(first, len(table))):
                 if table[j] != RELEASED:
                     grp.pool.free(table[j])
                     table[j] = RELEASED

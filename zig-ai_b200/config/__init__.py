@@ -1,6 +1,7 @@
 from .base import (ConfigError, ModelConfig, config_from_dict, known_architectures, load_config,
                    lookup_architecture, register_architecture, save_config, unregister_architecture)
 from .lfm2 import Lfm2Config, adjusted_ff_dim
+from .lolivik import LolivikConfig
 from .pikasun import PikasunConfig
 from .vunolorn import VunolornConfig
 from .zikevik import ZikevikConfig

@@ -60,6 +60,25 @@ __device__ __forceinline__ float zai_activate(float v, int kind) {
     }
 }
 
+// act(gate) * up on the stacked gate|up rows, for any of the activations above (SiLU has kernels of its own)
+template <typename T>
+__global__ void act_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int F, size_t total, int kind) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t t = i / F, f = i % F;
+    out[i] = from_float<T>(zai_activate(to_float(gu[t * 2 * F + f]), kind) * to_float(gu[t * 2 * F + F + f]));
+}
+
+ZAI_API int zai_act_mul(void* out, const void* gu, int dtype, int N, int F, int kind, cudaStream_t stream) {
+    const size_t total = (size_t)N * F;
+    if (total == 0) return ZAI_OK;
+    if (kind < 0 || kind > 3) return ZAI_BAD_SIZE;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    ZAI_DISPATCH(dtype, return launch_pdl(act_mul_kernel<T>, dim3(blocks), dim3(256), 0, stream, (T*)out, (const T*)gu, F, total, kind));
+}
+
 template <typename T>
 __global__ void activation_kernel(T* __restrict__ out, const T* __restrict__ in, int kind, size_t total) {
     pdl_trigger();

@@ -12,14 +12,29 @@
 // for the weighted sum.  Keys are always visited from the first visible position in steps of 32,
 // so a row's result does not depend on how the request was cut into steps or on its batch.
 // Pages: [num_pages, 2, Hkv, page_size, D].
+//
+// Options of designs that shape their scores (`ZaiScoreOptions`, all off by default):
+//   softcap     s <- cap * tanh(s / cap), before anything is added
+//   bias        s <- s + bias[min(pos - j, bias_rows - 1), head]: a table by distance (made on the host from the
+//               design's buckets), added after the cap and not scaled
+//   sink        one more term exp(sink[head]) in the softmax's denominator, with no key and no value
+//   keep_first  with a window: the first keep_first positions of the request stay visible (at their true positions)
 #include "common.cuh"
 
-template <typename T, int MAXR>
+struct ZaiScoreOptions {
+    float softcap;
+    const float* bias;
+    int bias_rows;
+    const float* sink;
+    int keep_first;
+};
+
+template <typename T, int MAXR, bool EXT>
 __global__ void paged_attention_warp_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ pages,
                                             const int* __restrict__ block_table, int table_width,
                                             const int* __restrict__ positions, const int* __restrict__ seq_idx,
                                             int page_size, int Hq, int Hkv, int D, float scale, int window,
-                                            int num_pages, int* __restrict__ status) {
+                                            int num_pages, int* __restrict__ status, const ZaiScoreOptions opt) {
     extern __shared__ float qs[];                 // [D]
     pdl_trigger();
     pdl_wait();
@@ -32,15 +47,19 @@ __global__ void paged_attention_warp_kernel(T* __restrict__ out, const T* __rest
     __syncwarp();
     const int kend = pos + 1;
     const int kstart = zai_first_visible(pos, window);
+    // kept first positions: the walk starts with them (in steps of 32 from position 0) and goes on at the window's start
+    const int kept = EXT && window > 0 ? min(opt.keep_first, kstart) : 0;
     const size_t page_stride = (size_t)2 * Hkv * page_size * D;
     const size_t v_off = (size_t)Hkv * page_size * D;
     float m = -INFINITY, l = 0.f;
     float acc[MAXR];
 #pragma unroll
     for (int r = 0; r < MAXR; ++r) acc[r] = 0.f;
-    for (int base = kstart; base < kend; base += 32) {
+    for (int part = kept > 0 ? 0 : 1; part < 2; ++part) {
+    const int stop = part == 0 ? kept : kend;
+    for (int base = part == 0 ? 0 : kstart; base < stop; base += 32) {
         const int j = base + lane;
-        const bool valid = j < kend;
+        const bool valid = j < stop;
         float s = -INFINITY;
         size_t krow = 0;
         if (valid) {
@@ -50,6 +69,10 @@ __global__ void paged_attention_warp_kernel(T* __restrict__ out, const T* __rest
             float dot = 0.f;
             for (int d = 0; d < D; ++d) dot += qs[d] * to_float(kp[d]);
             s = dot;
+            if (EXT) {
+                if (opt.softcap > 0.f) s = opt.softcap * tanhf(s / opt.softcap);
+                if (opt.bias) s += opt.bias[(size_t)min(pos - j, opt.bias_rows - 1) * Hq + h];
+            }
         }
         const float m_new = fmaxf(m, warp_max(s));
         const float p = valid ? expf(s - m_new) : 0.f;
@@ -57,7 +80,7 @@ __global__ void paged_attention_warp_kernel(T* __restrict__ out, const T* __rest
         l = l * corr + warp_sum(p);
 #pragma unroll
         for (int r = 0; r < MAXR; ++r) acc[r] *= corr;
-        const int n = min(32, kend - base);
+        const int n = min(32, stop - base);
         for (int jj = 0; jj < n; ++jj) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const unsigned long long rj = __shfl_sync(0xffffffffu, (unsigned long long)krow, jj);
@@ -69,6 +92,14 @@ __global__ void paged_attention_warp_kernel(T* __restrict__ out, const T* __rest
             }
         }
         m = m_new;
+    }
+    }
+    if (EXT && opt.sink) {                                  // the sink: a term of the denominator alone
+        const float sk = opt.sink[h], m_new = fmaxf(m, sk);
+        const float corr = expf(m - m_new);
+        l = l * corr + expf(sk - m_new);
+#pragma unroll
+        for (int r = 0; r < MAXR; ++r) acc[r] *= corr;
     }
     const float inv = 1.f / l;
     T* orow = out + ((size_t)t * Hq + h) * D;
@@ -83,22 +114,51 @@ ZAI_API int zai_paged_attention_general(void* out, const void* q, const void* pa
                                         int table_width, const int* positions, const int* seq_idx, int page_size,
                                         int N, int Hq, int Hkv, int D, float scale, int window, int num_pages, int* status,
                                         cudaStream_t stream) {
+    const ZaiScoreOptions opt = {0.f, nullptr, 0, nullptr, 0};
     if (N <= 0) return ZAI_OK;
     if (D < 1 || D > 512 || Hkv < 1 || Hq % Hkv != 0 || Hq > 65535) return ZAI_BAD_SIZE;
     const dim3 grid(N, Hq);
     const size_t smem = (size_t)D * sizeof(float);
     if (D <= 64) {
-        ZAI_DISPATCH(dtype, return launch_pdl(paged_attention_warp_kernel<T, 2>, grid, dim3(32), smem, stream,
+        ZAI_DISPATCH(dtype, return launch_pdl(paged_attention_warp_kernel<T, 2, false>, grid, dim3(32), smem, stream,
             (T*)out, (const T*)q, (const T*)pages, block_table, table_width, positions, seq_idx, page_size, Hq, Hkv,
-            D, scale, window, num_pages, status));
+            D, scale, window, num_pages, status, opt));
     } else if (D <= 256) {
-        ZAI_DISPATCH(dtype, return launch_pdl(paged_attention_warp_kernel<T, 8>, grid, dim3(32), smem, stream,
+        ZAI_DISPATCH(dtype, return launch_pdl(paged_attention_warp_kernel<T, 8, false>, grid, dim3(32), smem, stream,
             (T*)out, (const T*)q, (const T*)pages, block_table, table_width, positions, seq_idx, page_size, Hq, Hkv,
-            D, scale, window, num_pages, status));
+            D, scale, window, num_pages, status, opt));
     } else {
-        ZAI_DISPATCH(dtype, return launch_pdl(paged_attention_warp_kernel<T, 16>, grid, dim3(32), smem, stream,
+        ZAI_DISPATCH(dtype, return launch_pdl(paged_attention_warp_kernel<T, 16, false>, grid, dim3(32), smem, stream,
             (T*)out, (const T*)q, (const T*)pages, block_table, table_width, positions, seq_idx, page_size, Hq, Hkv,
-            D, scale, window, num_pages, status));
+            D, scale, window, num_pages, status, opt));
+    }
+    return launch_status();
+}
+
+// The same with the score options above.
+ZAI_API int zai_paged_attention_scored(void* out, const void* q, const void* pages, int dtype, const int* block_table,
+                                        int table_width, const int* positions, const int* seq_idx, int page_size,
+                                        int N, int Hq, int Hkv, int D, float scale, int window, int num_pages, int* status,
+                                        float softcap, const float* bias, int bias_rows, const float* sink, int keep_first,
+                                        cudaStream_t stream) {
+    if (softcap < 0.f || (bias && bias_rows < 1) || keep_first < 0 || (keep_first && window <= 0)) return ZAI_BAD_SIZE;
+    const ZaiScoreOptions opt = {softcap, bias, bias_rows, sink, keep_first};
+    if (N <= 0) return ZAI_OK;
+    if (D < 1 || D > 512 || Hkv < 1 || Hq % Hkv != 0 || Hq > 65535) return ZAI_BAD_SIZE;
+    const dim3 grid(N, Hq);
+    const size_t smem = (size_t)D * sizeof(float);
+    if (D <= 64) {
+        ZAI_DISPATCH(dtype, return launch_pdl(paged_attention_warp_kernel<T, 2, true>, grid, dim3(32), smem, stream,
+            (T*)out, (const T*)q, (const T*)pages, block_table, table_width, positions, seq_idx, page_size, Hq, Hkv,
+            D, scale, window, num_pages, status, opt));
+    } else if (D <= 256) {
+        ZAI_DISPATCH(dtype, return launch_pdl(paged_attention_warp_kernel<T, 8, true>, grid, dim3(32), smem, stream,
+            (T*)out, (const T*)q, (const T*)pages, block_table, table_width, positions, seq_idx, page_size, Hq, Hkv,
+            D, scale, window, num_pages, status, opt));
+    } else {
+        ZAI_DISPATCH(dtype, return launch_pdl(paged_attention_warp_kernel<T, 16, true>, grid, dim3(32), smem, stream,
+            (T*)out, (const T*)q, (const T*)pages, block_table, table_width, positions, seq_idx, page_size, Hq, Hkv,
+            D, scale, window, num_pages, status, opt));
     }
     return launch_status();
 }

@@ -59,7 +59,8 @@ __device__ __forceinline__ bool moe_rows_aligned(const T* p, size_t stride, int 
 template <typename T>
 __global__ void __launch_bounds__(128) moe_route_kernel(int* __restrict__ ids, float* __restrict__ wts, int* __restrict__ rank,
                                                         int* __restrict__ counts, const T* __restrict__ x, int x_stride,
-                                                        const float* __restrict__ wr, int W, int E, int top, int renorm) {
+                                                        const float* __restrict__ wr, int W, int E, int top, int renorm,
+                                                        int softmax) {
     extern __shared__ float sc[];                        // [E] scores
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_trigger();
@@ -82,10 +83,20 @@ __global__ void __launch_bounds__(128) moe_route_kernel(int* __restrict__ ids, f
             for (int c = lane; c < W; c += 32) acc += to_float(row[c]) * w[c];
         }
         acc = warp_sum(acc);
-        if (lane == 0) sc[e] = 1.f / (1.f + expf(-acc));
+        if (lane == 0) sc[e] = softmax ? acc : 1.f / (1.f + expf(-acc));
     }
     __syncthreads();
     if (warp != 0) return;
+    if (softmax) {                                       // scores = softmax of the logits over all experts, in a fixed order
+        float top_z = -INFINITY;
+        for (int e = lane; e < E; e += 32) top_z = fmaxf(top_z, sc[e]);
+        top_z = warp_max(top_z);
+        float total = 0.f;
+        for (int e = lane; e < E; e += 32) total += expf(sc[e] - top_z);
+        total = warp_sum(total);
+        for (int e = lane; e < E; e += 32) sc[e] = expf(sc[e] - top_z) / total;
+        __syncwarp();
+    }
     float sum = 0.f;
     for (int k = 0; k < top; ++k) {
         float best = -1.f;
@@ -111,7 +122,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(int* __restrict__ ids, f
         __syncwarp();
     }
     __syncwarp();
-    if (renorm && lane < top) wts[(size_t)t * top + lane] /= sum;
+    if (renorm && lane < top) wts[(size_t)t * top + lane] /= sum + 1e-20f;
 }
 
 // ------------------------------------------------------------------------------------------------ gather
@@ -171,6 +182,17 @@ template <> __device__ __forceinline__ void moe_store<float>(float* p, float v) 
 template <> __device__ __forceinline__ void moe_store<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
 
 __device__ __forceinline__ float moe_silu(float g) { return g / (1.f + expf(-g)); }
+// The gated epilogues: 1  silu(g) u;  2  g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit)
+struct MoeAct {
+    int kind;
+    float limit, alpha;
+    __device__ __forceinline__ float operator()(float g, float u) const {
+        if (kind != 2) return moe_silu(g) * u;
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.f + expf(-alpha * g)) * (u + 1.f);
+    }
+};
 
 // The weight row that row r (0..63) of a block's tile of weights holds, or -1.  Plain: output column n0 + r.  Gated:
 // groups of eight rows alternate between the gate and the up rows of the same eight features.
@@ -186,7 +208,7 @@ __device__ __forceinline__ int moe_weight_row(int r, int col_block, int n_out, i
 template <int TM, typename TO>
 __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(TO* __restrict__ out, const bf16* __restrict__ xs,
                                                            const bf16* __restrict__ w, const int* __restrict__ tile_expert,
-                                                           int K, int n_out, int gated) {
+                                                           int K, int n_out, int gated, const MoeAct act) {
     constexpr int WM = TM / 16, WN = 4 / WM, NT = 8 / WN;            // warps along rows and columns; 8-column tiles a warp
     __shared__ __align__(16) bf16 sa[MOE_STAGES][TM][MOE_ST];
     __shared__ __align__(16) bf16 sb[MOE_STAGES][MOE_TN][MOE_ST];
@@ -251,8 +273,8 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(TO* __restrict__ out,
             for (int c = 0; c < 2; ++c) {
                 const int f = blockIdx.y * (MOE_TN / 2) + (wn * (NT / 2) + np) * 8 + 2 * tq + c;
                 if (f < n_out) {
-                    moe_store<TO>(out + ra * n_out + f, moe_silu(acc[np * 2][c]) * acc[np * 2 + 1][c]);
-                    moe_store<TO>(out + rb * n_out + f, moe_silu(acc[np * 2][2 + c]) * acc[np * 2 + 1][2 + c]);
+                    moe_store<TO>(out + ra * n_out + f, act(acc[np * 2][c], acc[np * 2 + 1][c]));
+                    moe_store<TO>(out + rb * n_out + f, act(acc[np * 2][2 + c], acc[np * 2 + 1][2 + c]));
                 }
             }
         }
@@ -274,7 +296,8 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(TO* __restrict__ out,
 // Any element type and any K: a tile of 16 rows x 64 columns by 32-bit multiply-adds, k in ascending order.
 template <typename T, typename TO>
 __global__ void __launch_bounds__(128) moe_gemm_plain_kernel(TO* __restrict__ out, const T* __restrict__ xs, const T* __restrict__ w,
-                                                             const int* __restrict__ tile_expert, int K, int n_out, int gated) {
+                                                             const int* __restrict__ tile_expert, int K, int n_out, int gated,
+                                                             const MoeAct act) {
     __shared__ float sa[16][MOE_TK + 1];
     __shared__ float sb[MOE_TN][MOE_TK + 1];
     pdl_trigger();
@@ -311,7 +334,7 @@ __global__ void __launch_bounds__(128) moe_gemm_plain_kernel(TO* __restrict__ ou
 #pragma unroll
         for (int j = 0; j < 8; j += 2) {
             const int f = blockIdx.y * (MOE_TN / 2) + (j / 2) * 8 + c8;
-            if (f < n_out) moe_store<TO>(out + (row0 + r) * n_out + f, moe_silu(acc[j]) * acc[j + 1]);
+            if (f < n_out) moe_store<TO>(out + (row0 + r) * n_out + f, act(acc[j], acc[j + 1]));
         }
         return;
     }
@@ -356,13 +379,13 @@ __global__ void moe_combine_kernel(T* __restrict__ out, const float* __restrict_
 // ------------------------------------------------------------------------------------------------ launchers
 // ids, rank [N, top] int; wts [N, top] 32-bit; counts [E] int, zeroed here; x [N, x_stride] in `dtype`; wr [E, W] 32-bit
 ZAI_API int zai_moe_route(int* ids, float* wts, int* rank, int* counts, const void* x, int x_stride, int dtype, const float* wr,
-                          int N, int W, int E, int top, int renorm, cudaStream_t stream) {
+                          int N, int W, int E, int top, int renorm, int softmax, cudaStream_t stream) {
     if (N <= 0) return ZAI_OK;
     if (E < 1 || top < 1 || top > E || top > 32 || E > 8192 || W < 1) return ZAI_BAD_SIZE;
     cudaError_t rc = cudaMemsetAsync(counts, 0, (size_t)E * sizeof(int), stream);
     if (rc != cudaSuccess) return (int)rc;
     ZAI_DISPATCH(dtype, return launch_pdl(moe_route_kernel<T>, dim3(N), dim3(128), (size_t)E * sizeof(float), stream, ids, wts, rank,
-                                          counts, (const T*)x, x_stride, wr, W, E, top, renorm));
+                                          counts, (const T*)x, x_stride, wr, W, E, top, renorm, softmax));
 }
 
 // The most tiles of TM rows that N x top choices over E experts can take.
@@ -385,17 +408,19 @@ ZAI_API int zai_moe_gather(void* xs, int* dest, int* tile_expert, const void* x,
 }
 
 // out [max_tiles * TM, n_out] (32-bit if out_f32, else `dtype`) = xs [max_tiles * TM, K] . w[expert of the tile]^T;
-// w [E, n_out, K], or with `gated` [E, 2 n_out, K] and out = silu(gate) * up.  TM 16 or 64 (the gather's).
+// w [E, n_out, K], or with `gated` [E, 2 n_out, K] and out = silu(gate) * up (gated 1) or the bounded gated activation with
+// `limit` and `alpha` (gated 2).  TM 16 or 64 (the gather's).
 ZAI_API int zai_moe_gemm(void* out, int out_f32, const void* xs, const void* w, int dtype, const int* tile_expert, int max_tiles,
-                         int TM, int K, int n_out, int gated, cudaStream_t stream) {
+                         int TM, int K, int n_out, int gated, float limit, float alpha, cudaStream_t stream) {
     if (max_tiles <= 0) return ZAI_OK;
+    const MoeAct act = {gated, limit, alpha};
     if (K < 1 || n_out < 1 || (TM != 16 && TM != 64)) return ZAI_BAD_SIZE;
     const int cols = gated ? MOE_TN / 2 : MOE_TN;
     const dim3 grid(max_tiles, (n_out + cols - 1) / cols);
     if (grid.y > 65535) return ZAI_BAD_SIZE;
     if (dtype == ZAI_BF16 && K % 8 == 0) {
 #define MOE_GO(TMV, TOV) return launch_pdl(moe_gemm_mma_kernel<TMV, TOV>, grid, dim3(128), 0, stream, (TOV*)out, (const bf16*)xs, \
-                                           (const bf16*)w, tile_expert, K, n_out, gated)
+                                           (const bf16*)w, tile_expert, K, n_out, gated, act)
         if (TM == 16) { if (out_f32) MOE_GO(16, float); else MOE_GO(16, bf16); }
         if (out_f32) MOE_GO(64, float); else MOE_GO(64, bf16);
 #undef MOE_GO
@@ -403,13 +428,13 @@ ZAI_API int zai_moe_gemm(void* out, int out_f32, const void* xs, const void* w, 
     if (TM != 16) return ZAI_BAD_SIZE;                   // the plain kernel's tiles are 16 rows high
     if (dtype == ZAI_BF16) {
         if (out_f32) return launch_pdl(moe_gemm_plain_kernel<bf16, float>, grid, dim3(128), 0, stream, (float*)out, (const bf16*)xs,
-                                       (const bf16*)w, tile_expert, K, n_out, gated);
+                                       (const bf16*)w, tile_expert, K, n_out, gated, act);
         return launch_pdl(moe_gemm_plain_kernel<bf16, bf16>, grid, dim3(128), 0, stream, (bf16*)out, (const bf16*)xs, (const bf16*)w,
-                          tile_expert, K, n_out, gated);
+                          tile_expert, K, n_out, gated, act);
     }
     if (dtype != ZAI_F32) return ZAI_BAD_DTYPE;
     return launch_pdl(moe_gemm_plain_kernel<float, float>, grid, dim3(128), 0, stream, (float*)out, (const float*)xs, (const float*)w,
-                      tile_expert, K, n_out, gated);
+                      tile_expert, K, n_out, gated, act);
 }
 
 // out [N, W] in `dtype` = sum over a row's choices of y[dest], times the choice's weight with `scale_output`

@@ -145,6 +145,42 @@ ZAI_API int zai_add_rmsnorm(float* h, const void* delta, const float* gamma, voi
     ZAI_DISPATCH(dtype, return launch_pdl(add_rmsnorm_kernel<T>, dim3(N), dim3(threads), 0, stream, h, (const T*)delta, gamma, (T*)out, eps, H));
 }
 
+// A block whose sublayers read the residual stream itself:  h += delta * rsqrt(mean(delta^2) + eps_d) * gamma_d  (or the
+// plain delta without gamma_d, or nothing without delta);  out = h rounded to the activations' dtype.  Sum and norm 32-bit.
+template <typename T>
+__global__ void add_normed_cast_kernel(float* __restrict__ h, const T* __restrict__ delta, const float* __restrict__ gamma_d,
+                                       float eps_d, T* __restrict__ out, int H) {
+    __shared__ float red[33];
+    pdl_trigger();
+    pdl_wait();
+    const size_t base = (size_t)blockIdx.x * H;
+    float inv_d = 1.f;
+    if (delta && gamma_d) {
+        float sd = 0.f;
+        for (int c = threadIdx.x; c < H; c += blockDim.x) {
+            const float d = to_float(delta[base + c]);
+            sd += d * d;
+        }
+        inv_d = rsqrtf(block_sum(sd, red) / (float)H + eps_d);
+    }
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = h[base + c];
+        if (delta) {
+            v += gamma_d ? to_float(delta[base + c]) * inv_d * gamma_d[c] : to_float(delta[base + c]);
+            h[base + c] = v;
+        }
+        out[base + c] = from_float<T>(v);
+    }
+}
+
+ZAI_API int zai_add_normed_cast(float* h, const void* delta, const float* gamma_d, float eps_d, void* out, int dtype, int N, int H,
+                                cudaStream_t stream) {
+    if (N <= 0) return ZAI_OK;
+    const int threads = H >= 2048 ? 512 : 256;
+    ZAI_DISPATCH(dtype, return launch_pdl(add_normed_cast_kernel<T>, dim3(N), dim3(threads), 0, stream, h, (const T*)delta, gamma_d,
+                                          eps_d, (T*)out, H));
+}
+
 // RMS norm of activation rows (not the residual stream): out[n, :] = x[n, :C] * rsqrt(mean(x^2) + eps) * gamma, the row
 // read from a column slice (row stride x_stride) in the activations' dtype, everything between in 32-bit.
 template <typename T>

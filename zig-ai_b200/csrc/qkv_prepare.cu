@@ -19,7 +19,8 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(
     const T* __restrict__ y, int y_stride, const float* __restrict__ q_gamma, const float* __restrict__ k_gamma, float eps,
     int scope, const float2* __restrict__ cs_table, int rot, const int* __restrict__ positions, const int* __restrict__ seq_idx,
     const int* __restrict__ block_table, int table_width, T* __restrict__ pages, int page_size, T* __restrict__ q_out,
-    int Hq, int Hkv, int D, int Dv, int Dp, int write, int num_pages, int* __restrict__ status) {
+    int Hq, int Hkv, int D, int Dv, int Dp, int write, int num_pages, int* __restrict__ status, float temp_coef, int temp_every,
+    const T* __restrict__ v_first, int v_first_stride, const float* __restrict__ v_lambda) {
     extern __shared__ float smem[];
     __shared__ float red[33];
     const int half = rot / 2;
@@ -66,34 +67,42 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(
         if (d < rot) return x[d - half] * sn[d - half] + x[d] * cs[d - half];
         return d < D ? x[d] : 0.f;
     };
+    const int pos = positions[t];
+    // the queries' temperature: 1 + coef * ln(floor((pos + 1) / every) + 1), a step function of the position
+    const float temp = temp_every > 0 ? 1.f + temp_coef * logf((float)((pos < 0 ? 0 : pos + 1) / temp_every + 1)) : 1.f;
     T* qrow = q_out + (size_t)t * Hq * Dp;
     for (int i = tid; i < Hq * Dp; i += blockDim.x) {
         const int h = i / Dp, d = i - h * Dp;
-        qrow[i] = from_float<T>(turned(buf + (size_t)h * D, d));
+        qrow[i] = from_float<T>(turned(buf + (size_t)h * D, d) * temp);
     }
     if (!write) return;
-    const int pos = positions[t];
     const int page = zai_checked_page(block_table + (size_t)seq_idx[t] * table_width, table_width,
                                       pos < 0 ? -1 : pos / page_size, num_pages, status);
     const int off = pos < 0 ? 0 : pos % page_size;
     T* kpage = pages + (size_t)page * 2 * Hkv * page_size * Dp;
     T* vpage = kpage + (size_t)Hkv * page_size * Dp;
     const T* vrow = row + nq + nk;
+    // values mixed with an earlier layer's values of the same token: (1 - lambda) v + lambda v_first, in 32-bit
+    const T* frow = v_first ? v_first + (size_t)t * v_first_stride : nullptr;
+    const float lam = frow ? v_lambda[0] : 0.f;
     for (int i = tid; i < Hkv * Dp; i += blockDim.x) {
         const int g = i / Dp, d = i - g * Dp;
         const size_t at = ((size_t)g * page_size + off) * Dp + d;
         kpage[at] = from_float<T>(turned(buf + nq + (size_t)g * D, d));
-        vpage[at] = d < Dv ? vrow[(size_t)g * Dv + d] : from_float<T>(0.f);
+        if (d >= Dv) vpage[at] = from_float<T>(0.f);
+        else if (!frow) vpage[at] = vrow[(size_t)g * Dv + d];
+        else vpage[at] = from_float<T>((1.f - lam) * to_float(vrow[(size_t)g * Dv + d]) + lam * to_float(frow[(size_t)g * Dv + d]));
     }
 }
 
 ZAI_API int zai_qkv_prepare(const void* y, int y_stride, int dtype, const float* q_gamma, const float* k_gamma, float eps, int scope,
                             const float2* cs_table, int rot, const int* positions, const int* seq_idx, const int* block_table,
                             int table_width, void* pages, int page_size, void* q_out, int N, int Hq, int Hkv, int D, int Dv,
-                            int Dp, int write, int num_pages, int* status, cudaStream_t stream) {
+                            int Dp, int write, int num_pages, int* status, float temp_coef, int temp_every, const void* v_first,
+                            int v_first_stride, const float* v_lambda, cudaStream_t stream) {
     if (N <= 0) return ZAI_OK;
     if (Hq < 1 || Hkv < 1 || D < 1 || Dv < 1 || Dp < D || Dp < Dv || rot < 0 || rot > D || rot % 2 || scope < 0 || scope > 2
-        || (scope && (!q_gamma || !k_gamma)) || (rot && !cs_table))
+        || (scope && (!q_gamma || !k_gamma)) || (rot && !cs_table) || temp_every < 0 || (v_first && !v_lambda))
         return ZAI_BAD_SIZE;
     const size_t smem = ((size_t)(Hq + Hkv) * D + rot) * sizeof(float);
     if (smem > 200 * 1024) return ZAI_BAD_SIZE;
@@ -106,7 +115,8 @@ ZAI_API int zai_qkv_prepare(const void* y, int y_stride, int dtype, const float*
     }
     ZAI_DISPATCH(dtype, return launch_pdl(qkv_prepare_kernel<T>, dim3(N), dim3(256), smem, stream, (const T*)y, y_stride, q_gamma,
                                           k_gamma, eps, scope, cs_table, rot, positions, seq_idx, block_table, table_width, (T*)pages,
-                                          page_size, (T*)q_out, Hq, Hkv, D, Dv, Dp, write, num_pages, status));
+                                          page_size, (T*)q_out, Hq, Hkv, D, Dv, Dp, write, num_pages, status, temp_coef, temp_every,
+                                          (const T*)v_first, v_first_stride, v_lambda));
     return launch_status();
 }
 

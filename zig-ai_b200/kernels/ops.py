@@ -33,15 +33,17 @@ _SIGNATURES = {
     },
     "norm": {"zai_add_rmsnorm": [_P, _P, _P, _P, _I, _F, _I, _I, _P],
              "zai_add_normed_rmsnorm": [_P, _P, _P, _F, _P, _P, _I, _F, _I, _I, _P],
+             "zai_add_normed_cast": [_P, _P, _P, _F, _P, _I, _I, _I, _P],
              "zai_rmsnorm_rows": [_P, _P, _I, _I, _P, _F, _I, _I, _P]},
-    "moe": {"zai_moe_route": [_P, _P, _P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _I, _P],
+    "moe": {"zai_moe_route": [_P, _P, _P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _I, _I, _P],
             "zai_moe_max_tiles": [_I, _I, _I, _I],
             "zai_moe_gather": [_P, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
-            "zai_moe_gemm": [_P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _P],
+            "zai_moe_gemm": [_P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _F, _P],
             "zai_moe_combine": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P]},
     "layernorm": {"zai_add_layernorm": [_P, _P, _P, _P, _P, _I, _F, _I, _I, _P]},
     "qkv_prepare": {
-        "zai_qkv_prepare": [_P, _I, _I, _P, _P, _F, _I, _P, _I, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+        "zai_qkv_prepare": [_P, _I, _I, _P, _P, _F, _I, _P, _I, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P,
+                            _F, _I, _P, _I, _P, _P],
         "zai_latent_prepare": [_P, _I, _P, _I, _I, _P, _F, _P, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P],
         "zai_sigmoid_gate": [_P, _P, ctypes.c_longlong, ctypes.c_longlong, _P, _I, _I, _I, _I, _I, _I, _P],
     },
@@ -52,6 +54,7 @@ _SIGNATURES = {
     },
     "activation": {"zai_silu_mul": [_P, _P, _I, _I, _I, _P],
                    "zai_clamped_glu": [_P, _P, _I, _I, _I, _F, _F, _P],
+                   "zai_act_mul": [_P, _P, _I, _I, _I, _I, _P],
                    "zai_scale_softcap": [_P, ctypes.c_longlong, _F, _F, _P],
                    "zai_activation": [_P, _P, _I, _I, ctypes.c_longlong, _P],
                    "zai_weighted_sum": [_P, _P, _P, _I, _F, _F, ctypes.c_longlong, _P]},
@@ -78,7 +81,10 @@ _SIGNATURES = {
     },
     "attention": {
         "zai_paged_attention_general": [_P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
+        "zai_paged_attention_scored": [_P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _F, _P, _I, _P, _I, _P],
     },
+    "mlstm": {"zai_mlstm": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _F, _P, _F, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I,
+                            _P]},
     "attention_mma": {
         "zai_attention_mma_supports": [_I, _I, _I],
         "zai_prefill_attention_mma": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
@@ -397,6 +403,22 @@ def add_rmsnorm(h, delta, w, eps, out_dtype, delta_gamma=None, delta_eps=0.0):
         return out
     _check(_fn("norm", "zai_add_rmsnorm")(_ptr(h), _ptr(delta), _ptr(w), _ptr(out), _dt(out), float(eps), N, H,
                                           _stream()), "add_rmsnorm")
+    return out
+
+
+@_timed("norm")
+def add_cast(h, delta, out_dtype, delta_gamma=None, delta_eps=0.0):
+    """h += delta (in place, 32-bit; with `delta_gamma` the pending term passes an RMS norm with that weight first; nothing
+    with no delta), then h rounded to `out_dtype`: the input of a sublayer that reads the residual stream itself."""
+    _cuda(h, delta, delta_gamma)
+    if h.dtype != torch.float32 or (delta_gamma is not None and delta_gamma.dtype != torch.float32):
+        raise KernelError("the residual stream and norm weights are 32-bit")
+    if delta is not None and delta.dtype != out_dtype:
+        raise KernelError("the pending term should have the model's dtype")
+    N, H = h.shape
+    out = torch.empty((N, H), dtype=out_dtype, device=h.device)
+    _check(_fn("norm", "zai_add_normed_cast")(_ptr(h), _ptr(delta), _ptr(delta_gamma), float(delta_eps), _ptr(out), _dt(out), N, H,
+                                              _stream()), "add_cast")
     return out
 
 
@@ -766,7 +788,15 @@ def inverse_frequencies(rotary_dim: int, theta: float, device, scaling=None) -> 
     if t is None:
         i = torch.arange(rotary_dim // 2, dtype=torch.float64)
         t = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -2.0 * i / rotary_dim)
-        if scaling is not None:
+        if scaling is not None and scaling[0] == "wavelength":
+            # by wavelength l = 2 pi / f: kept below original / high, divided by factor above original / low, between the
+            # two mixed linearly in original / l
+            _, factor, low, high, original = scaling
+            wave = 2.0 * math.pi / t
+            smooth = (original / wave - low) / (high - low)
+            mixed = (1.0 - smooth) * t / factor + smooth * t
+            t = torch.where(wave < original / high, t, torch.where(wave > original / low, t / factor, mixed))
+        elif scaling is not None:
             factor, original, fast, slow = (float(v) for v in scaling)
             where = lambda turns: rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(float(theta)))
             lo = max(math.floor(where(fast)), 0)
@@ -780,7 +810,7 @@ def inverse_frequencies(rotary_dim: int, theta: float, device, scaling=None) -> 
 
 def rotation_magnitude(scaling) -> float:
     """The factor on cosines and sines of a stretched rotation: 0.1 ln(factor) + 1."""
-    return 1.0 if scaling is None else 0.1 * math.log(float(scaling[0])) + 1.0
+    return 1.0 if scaling is None or scaling[0] == "wavelength" else 0.1 * math.log(float(scaling[0])) + 1.0
 
 
 @_timed("q/k norm, rotation, page write")
@@ -851,14 +881,33 @@ def _attention_tickets(device, n):
     return t
 
 @_timed("attention")
-def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=None, impl=None, chunk=None):
+def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=None, impl=None, chunk=None, softcap=None, bias=None,
+                    sink=None, keep_first=0):
     """Causal attention of the step's rows over their requests' pages.  bfloat16 runs on the
     tensor cores (a split-key kernel when every span is one token, else the flash-style kernel)
     for the head sizes those kernels have; everything else, and `impl="general"`, runs the
     general kernel.  `impl="mma"` / `impl="tcgen05"` pick between the two span kernels.
     `window`: a query sees the last `window` positions; `chunk`: it sees back to the start of its chunk of that
-    many positions (the kernels take the chunk as a negative window)."""
-    _cuda(q)
+    many positions (the kernels take the chunk as a negative window).
+    Shaped scores (the general kernel): `softcap` (s <- cap tanh(s / cap)), `bias` [distances, heads] 32-bit (added after the
+    cap by min(distance, last row)), `sink` [heads] 32-bit (a term of the denominator alone), `keep_first` (with a window:
+    the request's first positions stay visible)."""
+    _cuda(q, bias, sink)
+    if softcap or bias is not None or sink is not None or keep_first:
+        if chunk is not None or (keep_first and not window):
+            raise KernelError("shaped scores go with a window or none; kept first positions need a window")
+        N = q.shape[0]
+        out = torch.empty((N, heads * head_dim), dtype=q.dtype, device=q.device)
+        bt = cache.block_table
+        if (cache.pages.dtype != q.dtype or N != step.n_tokens or (bias is not None and (bias.dtype != torch.float32 or bias.shape[1] != heads))
+                or (sink is not None and (sink.dtype != torch.float32 or sink.numel() != heads))):
+            raise KernelError("paged_attention: operands do not fit together")
+        _check(_fn("attention", "zai_paged_attention_scored")(
+            _ptr(out), _ptr(q), _ptr(cache.pages), _dt(q), _ptr(bt), bt.shape[1], _ptr(step.positions), _ptr(step.seq_idx),
+            cache.page_size, N, heads, kv_heads, head_dim, float(scale), int(window or 0), cache.pages.shape[0],
+            _status_ptr(q.device), float(softcap or 0.0), _ptr(bias), 0 if bias is None else bias.shape[0], _ptr(sink),
+            int(keep_first or 0), _stream()), "paged_attention (scored)")
+        return out
     if chunk is not None:
         if window is not None:
             raise KernelError("a window and chunks exclude each other")
@@ -1237,11 +1286,18 @@ def add_layernorm(h, delta, w, b, eps, out_dtype):
 
 
 @_timed("q/k norm, rotation, page write")
-def qkv_prepare(y, q_w, k_w, eps, scope, table, rot, step, cache, heads, kv_heads, dim, vdim, cache_dim, write=True):
+def qkv_prepare(y, q_w, k_w, eps, scope, table, rot, step, cache, heads, kv_heads, dim, vdim, cache_dim, write=True, temp=None,
+                v_first=None, v_lambda=None):
     """From projection rows y = [q (H D) | k (G D) | v (G Dv) | ...]: the RMS norm of q and k (`scope` 0 none, 1 per head,
     2 over the whole projection), the rotation of pairs (i, i + rot/2) from `table`, k and v into the pages (heads
-    `cache_dim` wide, zeros behind their own values); returns q [N, H * cache_dim]."""
-    _cuda(q_w, k_w, table)
+    `cache_dim` wide, zeros behind their own values); returns q [N, H * cache_dim].  `temp` = (coef, every): the queries times
+    1 + coef ln(floor((position + 1) / every) + 1).  `v_first` [N, G * Dv] (a column slice is fine) with `v_lambda` (one 32-bit
+    number on the device): the values cached are (1 - lambda) v + lambda v_first."""
+    _cuda(q_w, k_w, table, v_lambda)
+    fp, fs = (None, 0) if v_first is None else _rows_view(v_first)
+    if v_first is not None and (v_first.dtype != y.dtype or v_first.shape != (y.shape[0], int(kv_heads) * int(vdim))
+                                or v_lambda is None or v_lambda.dtype != torch.float32):
+        raise KernelError("qkv_prepare: the first values do not fit this layer's")
     yp, ys = _rows_view(y)
     N = y.shape[0]
     H, G, D, Dv, Dp = int(heads), int(kv_heads), int(dim), int(vdim), int(cache_dim)
@@ -1254,7 +1310,8 @@ def qkv_prepare(y, q_w, k_w, eps, scope, table, rot, step, cache, heads, kv_head
     _check(_fn("qkv_prepare", "zai_qkv_prepare")(
         yp, ys, _dt(y), _ptr(q_w), _ptr(k_w), float(eps), int(scope), _ptr(table), int(rot), _ptr(step.positions), _ptr(step.seq_idx),
         _ptr(bt), bt.shape[1], _ptr(pages), cache.page_size, _ptr(q), N, H, G, D, Dv, Dp, int(bool(write)), pages.shape[0],
-        _status_ptr(y.device), _stream()), "qkv_prepare")
+        _status_ptr(y.device), float(temp[0]) if temp else 0.0, int(temp[1]) if temp else 0, fp, fs, _ptr(v_lambda) if fp else None,
+        _stream()), "qkv_prepare")
     return q
 
 
@@ -1405,11 +1462,17 @@ MOE_TALL_TILE_ROWS = 32      # from this many rows per expert on average, tiles 
 
 
 @_timed("experts")
-def routed_experts(x, w_router, w_gate_up, w_down, top, renorm=False, weight_on="input"):
+def routed_experts(x, w_router, w_gate_up, w_down, top, renorm=False, weight_on="input", score="sigmoid", act="silu", limit=0.0,
+                   alpha=1.702):
     """A mixture of gated feed-forwards.  x [N, W]; w_router [E, W] 32-bit; w_gate_up [E, 2 F, W] (an expert's gate rows,
     then its up rows); w_down [E, W, F].  Every row goes to the `top` experts with the largest sigmoid(x . w_router^T)
     (32-bit); the scores are the weights (divided by their sum with `renorm`), applied to the expert's input or to its
-    output; the row's results are summed in 32-bit.  Nothing is read back to the host."""
+    output; the row's results are summed in 32-bit.  Nothing is read back to the host.  `score="softmax"`: the scores are the
+    softmax of the router's logits over all experts (`renorm` divides by the chosen scores' sum + 1e-20).  `act="clamped"`:
+    the experts are bounded gated units min(g, limit) sigmoid(alpha min(g, limit)) (clamp(u, -limit, limit) + 1)."""
+    if score not in ("sigmoid", "softmax") or act not in ("silu", "clamped"):
+        raise KernelError("routed_experts: score is sigmoid or softmax, act silu or clamped")
+    gated = 2 if act == "clamped" else 1
     _cuda(w_router, w_gate_up, w_down)
     xp, xs = _rows_view(x)
     N, W = x.shape
@@ -1426,7 +1489,7 @@ def routed_experts(x, w_router, w_gate_up, w_down, top, renorm=False, weight_on=
     tall = dt == _BF16 and W % 8 == 0 and F % 8 == 0 and N * top >= MOE_TALL_TILE_ROWS * E
     # many rows an expert: tiles of 128 rows and both products on the 5th-generation tensor cores (grouped tcgen05)
     grouped = (tall and USE_MOE_GROUPED_TC and N * top >= MOE_GROUPED_TILE_ROWS * E
-               and _fn("gemm_tc", "zai_gemm_tc_supports")(128, 2 * F, W, _EPI_SWIGLU)
+               and _fn("gemm_tc", "zai_gemm_tc_supports")(128, 2 * F, W, _EPI_SWIGLU if act == "silu" else _EPI_BF16)
                and _fn("gemm_tc", "zai_gemm_tc_supports")(128, W, F, _EPI_F32))
     TM = 128 if grouped else 64 if tall else 16
     max_tiles = _fn(lib, "zai_moe_max_tiles")(N, top, E, TM)
@@ -1438,27 +1501,78 @@ def routed_experts(x, w_router, w_gate_up, w_down, top, renorm=False, weight_on=
     counts, tile_expert = meta[4 * N * top:4 * N * top + E], meta[4 * N * top + E:]
     on_input = int(weight_on == "input")
     _check(_fn(lib, "zai_moe_route")(_ptr(ids), _ptr(wts), _ptr(rank), _ptr(counts), xp, xs, dt, _ptr(w_router), N, W, E, top,
-                                     int(bool(renorm)), _stream()), "moe_route")
+                                     int(bool(renorm)), int(score == "softmax"), _stream()), "moe_route")
     rows = max_tiles * TM
     x_sorted = torch.empty((rows, W), dtype=x.dtype, device=dev)
     _check(_fn(lib, "zai_moe_gather")(_ptr(x_sorted), _ptr(dest), _ptr(tile_expert), xp, xs, dt, _ptr(ids), _ptr(wts), _ptr(rank),
                                       _ptr(counts), N, W, E, top, TM, max_tiles, on_input, _stream()), "moe_gather")
-    act = torch.empty((rows, F), dtype=x.dtype, device=dev)
+    hidden = torch.empty((rows, F), dtype=x.dtype, device=dev)
     y = torch.empty((rows, W), dtype=torch.float32, device=dev)
     if grouped:
         tc = _fn("gemm_tc", "zai_gemm_tc_grouped")
-        _check(tc(_ptr(act), _ptr(w_gate_up), _ptr(x_sorted), _ptr(tile_expert), _status_ptr(dev), max_tiles, E, 2 * F, W,
-                  _EPI_SWIGLU, _stream()), "gemm_tc_grouped (gate/up)")
-        _check(tc(_ptr(y), _ptr(w_down), _ptr(act), _ptr(tile_expert), _status_ptr(dev), max_tiles, E, W, F,
+        if gated == 2:        # the plain grouped product, then the bounded activation on its gate|up rows
+            gu = torch.empty((rows, 2 * F), dtype=x.dtype, device=dev)
+            _check(tc(_ptr(gu), _ptr(w_gate_up), _ptr(x_sorted), _ptr(tile_expert), _status_ptr(dev), max_tiles, E, 2 * F, W,
+                      _EPI_BF16, _stream()), "gemm_tc_grouped (gate/up)")
+            hidden = clamped_glu(gu, F, limit, alpha)
+        else:
+            _check(tc(_ptr(hidden), _ptr(w_gate_up), _ptr(x_sorted), _ptr(tile_expert), _status_ptr(dev), max_tiles, E, 2 * F, W,
+                      _EPI_SWIGLU, _stream()), "gemm_tc_grouped (gate/up)")
+        _check(tc(_ptr(y), _ptr(w_down), _ptr(hidden), _ptr(tile_expert), _status_ptr(dev), max_tiles, E, W, F,
                   _EPI_F32_PAIR if USE_MOE_DOWN_PAIR else _EPI_F32, _stream()),
                "gemm_tc_grouped (down)")
         _check(_fn(lib, "zai_moe_combine")(_ptr(out), dt, _ptr(y), _ptr(dest), _ptr(wts), N, W, top, 1 - on_input, _stream()),
                "moe_combine")
         return out
-    _check(_fn(lib, "zai_moe_gemm")(_ptr(act), int(dt == _F32), _ptr(x_sorted), _ptr(w_gate_up), dt, _ptr(tile_expert), max_tiles,
-                                    TM, W, F, 1, _stream()), "moe_gemm (gate/up)")
-    _check(_fn(lib, "zai_moe_gemm")(_ptr(y), 1, _ptr(act), _ptr(w_down), dt, _ptr(tile_expert), max_tiles, TM, F, W, 0, _stream()),
-           "moe_gemm (down)")
+    _check(_fn(lib, "zai_moe_gemm")(_ptr(hidden), int(dt == _F32), _ptr(x_sorted), _ptr(w_gate_up), dt, _ptr(tile_expert), max_tiles,
+                                    TM, W, F, gated, float(limit), float(alpha), _stream()), "moe_gemm (gate/up)")
+    _check(_fn(lib, "zai_moe_gemm")(_ptr(y), 1, _ptr(hidden), _ptr(w_down), dt, _ptr(tile_expert), max_tiles, TM, F, W, 0, 0.0, 0.0,
+                                    _stream()), "moe_gemm (down)")
     _check(_fn(lib, "zai_moe_combine")(_ptr(out), dt, _ptr(y), _ptr(dest), _ptr(wts), N, W, top, 1 - on_input, _stream()),
            "moe_combine")
+    return out
+
+
+# ----------------------------------------------------------------------------- gated feed-forward with any activation, mLSTM
+_ACT_KINDS = {"gelu": 0, "gelu_erf": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
+
+
+@_timed("activation")
+def act_mul(gu, ff_dim, kind):
+    """act(gate) * up on the stacked gate|up rows; `kind` as in `activation`."""
+    _cuda(gu)
+    if kind not in _ACT_KINDS:
+        raise KernelError(f"unknown activation '{kind}'")
+    N = gu.shape[0]
+    out = torch.empty((N, ff_dim), dtype=gu.dtype, device=gu.device)
+    _check(_fn("activation", "zai_act_mul")(_ptr(out), _ptr(gu), _dt(gu), N, int(ff_dim), _ACT_KINDS[kind], _stream()), "act_mul")
+    return out
+
+
+def linear_glu(x, w_gate_up, ff_dim, kind):
+    """The stacked gate|up product (x may be a LazyNorm) and act(gate) * up; SiLU takes the fused ways of `linear_swiglu`."""
+    if kind == "silu":
+        return linear_swiglu(x, w_gate_up, ff_dim)
+    return act_mul(linear(x, w_gate_up), ff_dim, kind)
+
+
+@_timed("recurrence")
+def mlstm(y, at, bias_i, bias_f, cap, norm_w, eps, state, step, heads, dim, vdim, write_state=True):
+    """The matrix memory with log gates.  y [N, cols]: the stacked projections, `at` the first columns of q (H D), k (H D), v (H
+    Dv), the output gate (H Dv) and the inputs of the log input and forget gates (H each); bias_i, bias_f [H], norm_w [H Dv]
+    32-bit; state [slots, H, D + 1, Dv + 1] 32-bit (the normaliser as the last column, every column's running maximum as
+    the last row).  Returns rms_per_head(o) * norm_w * sigmoid(gate), [N, H Dv]."""
+    _cuda(bias_i, bias_f, norm_w, state)
+    yp, ys = _rows_view(y)
+    N, H, D, Dv = y.shape[0], int(heads), int(dim), int(vdim)
+    if (state.dtype != torch.float32 or tuple(state.shape[1:]) != (H, D + 1, Dv + 1) or bias_i.dtype != torch.float32
+            or bias_f.dtype != torch.float32 or norm_w.dtype != torch.float32 or norm_w.numel() != H * Dv or N != step.n_tokens):
+        raise KernelError("mlstm: operands do not fit together")
+    out = torch.empty((N, H * Dv), dtype=y.dtype, device=y.device)
+    part = torch.empty((N, H, Dv + 2), dtype=torch.float32, device=y.device)
+    q_at, k_at, v_at, g_at, i_at, f_at = (int(a) for a in at)
+    _check(_fn("mlstm", "zai_mlstm")(_ptr(out), _ptr(part), yp, ys, _dt(y), q_at, k_at, v_at, g_at, i_at, f_at, _ptr(bias_i),
+                                     _ptr(bias_f), float(cap), _ptr(norm_w), float(eps), _ptr(state), _ptr(step.cu_q),
+                                     _ptr(step.slot_ids), state.shape[0], _status_ptr(y.device), N, step.n_seqs, H, D, Dv,
+                                     int(bool(write_state)), _stream()), "mlstm", 2)
     return out

@@ -1,6 +1,6 @@
 """Architectures: each module registers its name, its config class and the function that lays out
 its layers from parts."""
-from . import lfm2, pikasun, vunolorn, zikevik  # noqa: F401  (registration)
+from . import lfm2, lolivik, pikasun, vunolorn, zikevik  # noqa: F401  (registration)
 from .model import Model
 from ..config.base import lookup_architecture
 

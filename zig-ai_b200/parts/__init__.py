@@ -4,4 +4,4 @@ from .base import (Block, Embedding, FeedForward, Head, LazyNorm, NormedTerm, Re
                    PagedKVNeed, PagedRowsNeed, ParamDecl, Part, PartSpec, PositionEncoding, StateNeed, make_block,
                    make_part, needs_of, register_part, unregister_part)
 from . import (norms, position, feed_forward, short_conv, attention, selective_scan, gated_delta, min_gru, parallel,  # noqa: F401
-               latent_attention, block, embedding)                                                                   # (registration)
+               latent_attention, mlstm, block, embedding)                                                                   # (registration)

@@ -23,6 +23,20 @@ the projections run as one product q|k|v|gate and one kernel norms, rotates and 
 (`ops.qkv_prepare`); an interleaved pairing is turned into the half-split one by reordering the rows of the q
 and k projections (with their biases and norm weights) at load.
 
+Options that shape the scores or the values (they also take the one-product path, and the general attention kernel):
+    q_temp=(coef, every)   the queries at position p times 1 + coef ln(floor((p + 1) / every) + 1)
+    softcap=c              s <- c tanh(s / c), after the scale and before anything is added
+    rel_bias={rows, max}   a learned table `rel` [rows, heads] added to the score by distance n = i - j: row n for n < rows/2,
+                           beyond that rows that widen geometrically, min(rows - 1, rows/2 + floor(ln(n / (rows/2)) /
+                           ln(max / (rows/2)) * (rows - rows/2))); not scaled, not capped.  The table is laid out by distance
+                           once at load (`distance_table`)
+    sink=True              a learned number per head `sink` whose exponential joins the softmax's denominator (no key, no value)
+    keep_first=n           with a window: the first n positions of the request stay visible to every later query, at their
+                           true positions; their pages are never given back
+    v_mix="first"|"mix"    values shared across layers: a "first" layer leaves its values with the step, a "mix" layer
+                           caches (1 - lambda) v + lambda v_first with its learned scalar `vmix` (the first layer's is stored
+                           and unused)
+
 Reference: projections src/transformer/hybrid_attn.zig:285-354, per-head norm :371-382 (device
 :719,723), scale 1/sqrt(D) :571, causal mask :587, softmax :578-600, query head hq reads kv head
 hq // (Hq/Hkv) :553-569 and src/cuda/paged_attention.cu:142, output projection :622-640; tensor
@@ -44,7 +58,8 @@ class Attention(Mixer):
 
     def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, qk_norm: bool, eps: float,
                  position: PartSpec, window=None, scale=None, kv_proj: bool = True, value_dim=None,
-                 value_norm: bool = False, names=None, bias: bool = False, norm_scope: str = "head", chunk=None, gate=None):
+                 value_norm: bool = False, names=None, bias: bool = False, norm_scope: str = "head", chunk=None, gate=None,
+                 q_temp=None, softcap=None, rel_bias=None, sink: bool = False, keep_first: int = 0, v_mix=None):
         self.hidden, self.heads, self.kv_heads, self.head_dim = int(hidden), int(heads), int(kv_heads), int(head_dim)
         if self.heads % self.kv_heads:
             raise ValueError(f"{self.heads} query heads cannot share {self.kv_heads} key/value heads evenly")
@@ -60,15 +75,30 @@ class Attention(Mixer):
         self.cache_dim = max(self.head_dim, self.value_dim)      # the head size of the pages and the kernels
         self.names = {"q": "attn_q.weight", "k": "attn_k.weight", "v": "attn_v.weight", "o": "attn_output.weight",
                       "q_norm": "attn_q_norm.weight", "k_norm": "attn_k_norm.weight", "q_bias": "attn_q.bias",
-                      "k_bias": "attn_k.bias", "v_bias": "attn_v.bias", "g": "attn_gate.weight", **(names or {})}
+                      "k_bias": "attn_k.bias", "v_bias": "attn_v.bias", "g": "attn_gate.weight", "rel": "attn_rel_bias",
+                      "sink": "attn_sink", "vmix": "attn_vmix", **(names or {})}
         self.bias, self.norm_scope, self.gate = bool(bias), str(norm_scope), gate
         self.chunk = None if chunk is None else int(chunk)
         if self.norm_scope not in ("head", "whole") or self.gate not in (None, "head"):
             raise ValueError("norm_scope is 'head' or 'whole'; gate is None or 'head'")
         if self.chunk is not None and (self.chunk < 1 or self.window is not None):
             raise ValueError("a chunk holds at least one position, and chunks and a window exclude each other")
+        self.q_temp = None if q_temp is None else (float(q_temp[0]), int(q_temp[1]))
+        self.softcap = None if softcap is None else float(softcap)
+        self.rel_bias = None if rel_bias is None else {"rows": int(rel_bias["rows"]), "max": float(rel_bias["max"])}
+        self.sink, self.keep_first, self.v_mix = bool(sink), int(keep_first or 0), v_mix
+        if self.v_mix not in (None, "first", "mix"):
+            raise ValueError("v_mix is None, 'first' or 'mix'")
+        if self.keep_first and self.window is None:
+            raise ValueError("kept first positions go with a window")
+        if self.q_temp is not None and self.q_temp[1] < 1:
+            raise ValueError("q_temp counts positions in groups of at least one")
+        if self.rel_bias is not None and (self.rel_bias["rows"] < 2 or self.rel_bias["max"] <= self.rel_bias["rows"] // 2):
+            raise ValueError("a distance-bias table has at least two rows and reaches beyond its one-distance rows")
+        self.shaped = bool(self.softcap or self.rel_bias or self.sink or self.keep_first)
         # the options that the one-product, one-preparation path serves
         self.prepared = bool(self.bias or self.norm_scope == "whole" or self.gate or self.chunk is not None
+                             or self.shaped or self.q_temp or self.v_mix
                              or getattr(self.position, "pairing", "half_split") != "half_split"
                              or getattr(self.position, "scaling", None) is not None)
         if self.prepared and (self.value_norm or not self.kv_proj):
@@ -95,10 +125,31 @@ class Attention(Mixer):
             p[nm["v_bias"]] = ParamDecl((self.kv_heads * self.value_dim,), "vector", init="conv")
         if self.gate:
             p[nm["g"]] = ParamDecl((self.heads, self.hidden))
+        if self.rel_bias:
+            p[nm["rel"]] = ParamDecl((self.rel_bias["rows"], self.heads), "vector", init="conv")
+        if self.sink:
+            p[nm["sink"]] = ParamDecl((self.heads,), "vector", init="conv")
+        if self.v_mix:
+            p[nm["vmix"]] = ParamDecl((), "vector", init="mix")
         return p
 
     def cache_need(self):
-        return PagedKVNeed(self.kv_heads, self.cache_dim, self.window, self.chunk)
+        return PagedKVNeed(self.kv_heads, self.cache_dim, self.window, self.chunk, self.keep_first)
+
+    def distance_table(self, rel):
+        """The bias by distance, [distances, heads]: row n holds `rel[bucket(n)]`; the last row stands for every distance
+        from there on (the first distance of the table's last bucket).  Made once at load, in 64-bit on the host."""
+        rows, far = self.rel_bias["rows"], self.rel_bias["max"]
+        half = rows // 2
+        buckets, n = [], 0
+        while True:
+            b = n if n < half else min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
+            buckets.append(b)
+            if b == rows - 1:
+                break
+            n += 1
+        idx = torch.tensor(buckets, dtype=torch.long, device=rel.device)
+        return rel.float().index_select(0, idx).contiguous()
 
     def _bind_prepared(self, tensors, dtype):
         """One matrix q|k|v|gate (and one bias vector), the rows of q and k in the order in which the rotation pairs
@@ -132,6 +183,10 @@ class Attention(Mixer):
             w = self.w_o.reshape(self.hidden, H, Dv)
             self.w_o = torch.cat([w, w.new_zeros(self.hidden, H, Dp - Dv)], dim=2).reshape(self.hidden, -1).contiguous()
         self.gate_at = H * D + G * D + G * Dv
+        self.v_at = H * D + G * D
+        self.bias_table = self.distance_table(tensors[nm["rel"]]) if self.rel_bias else None
+        self.sink_w = tensors[nm["sink"]].float().contiguous() if self.sink else None
+        self.v_lambda = tensors[nm["vmix"]].float().reshape(1).contiguous() if self.v_mix == "mix" else None
         self.dtype = dtype
 
     def _forward_prepared(self, x, step, cache, write_cache):
@@ -139,9 +194,22 @@ class Attention(Mixer):
         y = ops.linear(x, self.w_qkv, bias=self.b_qkv)
         dims, table = self.position.table(step, y.device)
         scope = 0 if not self.qk_norm else (2 if self.norm_scope == "whole" else 1)
+        more = {}
+        if self.q_temp:
+            more["temp"] = self.q_temp
+        if self.v_mix == "first":
+            step.scratch["attention.v_first"] = y[:, self.v_at:self.v_at + G * Dv]     # (kept alive with the step)
+        elif self.v_mix == "mix":
+            if "attention.v_first" not in step.scratch:
+                raise RuntimeError("a layer mixes its values with an earlier layer's, and no earlier layer has left any")
+            more.update(v_first=step.scratch["attention.v_first"], v_lambda=self.v_lambda)
         q = ops.qkv_prepare(y, self.q_norm, self.k_norm, self.norm_eps, scope, table, dims, step, cache, H, G, D, Dv, Dp,
-                            write_cache)
-        o = ops.paged_attention(q, step, cache, H, G, Dp, self.scale, self.window, chunk=self.chunk)
+                            write_cache, **more)
+        if self.shaped:
+            o = ops.paged_attention(q, step, cache, H, G, Dp, self.scale, self.window, softcap=self.softcap, bias=self.bias_table,
+                                    sink=self.sink_w, keep_first=self.keep_first)
+        else:
+            o = ops.paged_attention(q, step, cache, H, G, Dp, self.scale, self.window, chunk=self.chunk)
         if self.gate:
             o = ops.sigmoid_gate(o, y[:, self.gate_at:self.gate_at + H], H, Dp, True)
         return ops.linear(o, self.w_o)

@@ -73,7 +73,7 @@ class ParamDecl:
     role: str = "matrix"
     alt_shapes: Tuple[Tuple[int, ...], ...] = ()   # other stored layouts accepted and reshaped
     init: str = "normal"    # random-weights mode: "normal" N(0, 0.02^2), "norm_weight" 1 + U(-0.1, 0.1),
-                            # "conv" N(0, 0.1^2)
+                            # "conv" N(0, 0.1^2), "mix" U(0.2, 0.8)
 
 
 # --------------------------------------------------------------------------- cache needs
@@ -90,6 +90,7 @@ class PagedKVNeed:
     head_dim: int
     window: Optional[int] = None
     chunk: Optional[int] = None
+    keep_first: int = 0         # with a window: the first positions of the request that stay visible (their pages are kept)
 
     def page_shape(self, page_size: int) -> Tuple[int, ...]:
         return (2, self.kv_heads, page_size, self.head_dim)
@@ -143,7 +144,7 @@ class NormedTerm:
     the norm behind a sublayer, the residual addition and the norm before the next sublayer are one kernel."""
 
     def __init__(self, data, gamma, eps: float):
-        self.data, self.gamma, self.eps = data, gamma, float(eps)
+        self.data, self.gamma, self.eps = data, gamma, float(eps)     # (a factor on the normed term is part of `gamma`)
 
 
 class LazyNorm:

@@ -72,5 +72,52 @@ class SandwichResidual(Block):
         return h, NormedTerm(f, self.ff_post_norm.weight, self.ff_post_norm.eps)
 
 
+class PostNormResidual(Block):
+    """A norm on each sublayer's output only, and a factor on the normed term; the sublayers read the residual stream itself:
+
+        h = h + mult * norm_a(mixer(h));   h = h + mult * norm_b(feed_forward(h))
+
+    A sublayer's output travels as a `NormedTerm` (the factor folded into the norm's weight, once, in 32-bit) into whatever
+    comes next: this block's next sublayer, the next block, or the model's final norm.  The kernel that adds it to the
+    32-bit stream also rounds the stream to the activations' dtype for the sublayer that reads it."""
+    graph_safe = True      # forward launches kernels only; nothing is read back to the host
+
+    def __init__(self, mixer, mixer_norm, feed_forward=None, ff_norm=None, mult: float = 1.0):
+        super().__init__()
+        self.mult = float(mult)
+        self.mixer = self.sub("mixer", "mixer", mixer)
+        self.mixer_norm = self.sub("mixer_norm", "norm", mixer_norm)
+        self.feed_forward = None
+        if feed_forward is not None:
+            self.feed_forward = self.sub("feed_forward", "feed_forward", feed_forward)
+            self.ff_norm = self.sub("ff_norm", "norm", ff_norm)
+        self._gammas = {}
+
+    def params(self):
+        return {}
+
+    def _term(self, data, norm):
+        g = self._gammas.get(id(norm))
+        if g is None or g[0] is not norm.weight:
+            g = self._gammas[id(norm)] = (norm.weight, (norm.weight.float() * self.mult).contiguous())
+        return NormedTerm(data, g[1], norm.eps)
+
+    @staticmethod
+    def _read(h, pending, step):
+        """Add what is pending and return the stream in the activations' dtype."""
+        if isinstance(pending, NormedTerm):
+            return step.ops.add_cast(h.data, pending.data, step.dtype, pending.gamma, pending.eps)
+        return step.ops.add_cast(h.data, pending, step.dtype)
+
+    def forward(self, h, pending, step, cache, write_cache=True):
+        m = self.mixer.forward(self._read(h, pending, step), step, self.cache_for(self.mixer, cache), write_cache)
+        term = self._term(m, self.mixer_norm)
+        if self.feed_forward is None:
+            return h, term
+        f = self.feed_forward.forward(self._read(h, term, step), step)
+        return h, self._term(f, self.ff_norm)
+
+
 register_part("block", "prenorm_residual", PreNormResidual)
+register_part("block", "postnorm_residual", PostNormResidual)
 register_part("block", "sandwich_residual", SandwichResidual)

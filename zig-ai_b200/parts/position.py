@@ -24,7 +24,12 @@ class RotaryHalfSplit(PositionEncoding):
         if self.rotary_dim % 2 or not 0 < self.rotary_dim <= self.head_dim:
             raise ValueError(f"rotary_dim {self.rotary_dim} should be even and at most head_dim {self.head_dim}")
         self.scaling = None
-        if scaling is not None:
+        if scaling is not None and scaling.get("kind") == "wavelength":
+            # frequencies stretched by their wavelength l = 2 pi / f: kept where l < original / high, divided by `factor`
+            # where l > original / low, and between the two mixed by s = (original / l - low) / (high - low):
+            # (1 - s) f / factor + s f.  Cosines and sines keep their size.
+            self.scaling = ("wavelength",) + tuple(float(scaling[k]) for k in ("factor", "low", "high", "original"))
+        elif scaling is not None:
             self.scaling = tuple(float(scaling[k]) for k in ("factor", "original", "fast", "slow"))
 
     def rotary(self):

@@ -29,6 +29,8 @@ def random_tensor(name: str, decl: ParamDecl, seed: int, store_dtype: torch.dtyp
     g.manual_seed((int(seed) * 0x9E3779B1 + zlib.crc32(name.encode("utf-8"))) % (2 ** 63))
     if decl.init == "norm_weight":
         t = 1.0 + (torch.rand(decl.shape, generator=g, dtype=torch.float32) * 0.2 - 0.1)
+    elif decl.init == "mix":
+        t = 0.2 + 0.6 * torch.rand(decl.shape, generator=g, dtype=torch.float32)
     elif decl.init == "conv":
         t = torch.randn(decl.shape, generator=g, dtype=torch.float32) * 0.1
     else:
