@@ -637,10 +637,10 @@ def mlstm(y, at, bias_i, bias_f, cap, norm_w, eps, state, step, heads, dim, vdim
     q_at, k_at, v_at, g_at, i_at, f_at = at
     q = _f(y[:, q_at:q_at + H * D]).reshape(N, H, D) * D ** -0.5
     k = _f(y[:, k_at:k_at + H * D]).reshape(N, H, D)
-    v = torch.cat([_f(y[:, v_at:v_at + H * Dv]).reshape(N, H, Dv), torch.ones(N, H, 1)], dim=-1)
+    v = torch.cat([_f(y[:, v_at:v_at + H * Dv]).reshape(N, H, Dv), torch.ones(N, H, 1, device=y.device)], dim=-1)
     gi = cap * torch.tanh((_f(y[:, i_at:i_at + H]) + bias_i) / cap)
     gf = torch.nn.functional.logsigmoid(cap * torch.tanh((_f(y[:, f_at:f_at + H]) + bias_f) / cap))
-    out = torch.zeros((N, H, Dv), dtype=torch.float32)
+    out = torch.zeros((N, H, Dv), dtype=torch.float32, device=y.device)
     for a, b, slot in _spans(step, state):
         S, m = state[slot][:, :D, :].clone(), state[slot][:, D, 0].clone()
         for t in range(a, b):

@@ -1,0 +1,225 @@
+"""The Lolivik design on the GPU, whole models against the plain implementation (tests/plain_lolivik.py): requests replayed
+through bin/trace_run whole, with the last tokens decoded one by one, in portions of changing size and mixed with other
+requests in a pool so small that pages and slots are used again, in 32-bit and in bfloat16; window edges, kept first
+positions, far keys, the sink and the bias by distance with attention made sharp; a matrix memory that keeps a far
+token; long decoding through the step graphs; greedy generation through the entry point and the command line."""
+import json
+import os
+import random
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_lolivik as P
+import traces
+from lolivik_configs import ALL, ONLY, PAGE_SIZE
+from test_lolivik_cpu import read_model, sharp_key, tokens, with_tensors
+from zig_ai_b200.config import config_from_dict
+from zig_ai_b200.weights import write_random_model
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": [70, 45, 128, 33, 7, 1, 2, 96], "B": [130, 61, 257, 40, 5, 1, 33, 90], "C": [300, 129, 64, 410, 1, 35]}
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    root = tmp_path_factory.mktemp("lolivik_gpu")
+    out = {}
+    for name, (cfg, seed) in list(ALL.items()) + [(k, (ONLY[k], 5)) for k in ("sharp_windowed", "sharp_attention", "memory")]:
+        d = str(root / name)
+        write_random_model(config_from_dict(cfg), seed, d, matrix_std="fan_in")
+        out[name] = d
+    return out
+
+
+@pytest.fixture(scope="module")
+def plain(models):
+    out = {}
+    for name in ALL:
+        cfg, tensors = read_model(models[name])
+        reqs = traces.requests_for(cfg["vocab"], LENGTHS[name], 78)
+        out[name] = (reqs, {k: P.forward(cfg, tensors, t).numpy() for k, t in reqs.items()})
+    return out
+
+
+def rows_of(got, tag, k, n):
+    return np.stack([got[(tag + k, p)] for p in range(n)])
+
+
+def check(got_rows, want_rows, dtype, where):
+    """32-bit: every row, strictly.  bfloat16: a 16-bit router may send a row to another expert than the 64-bit one where two
+    scores lie closer than the input's rounding, and what that row leaves in the cache and the state moves the rows after it;
+    so half of the rows are held tightly and the share of rows that are far off is bounded.  The 32-bit run of the same
+    schedule holds every row, through the same cache and batch code."""
+    if dtype == "float32":
+        traces.check_request(got_rows, want_rows, dtype, where)
+        return
+    e = traces.request_errors(got_rows, want_rows)
+    assert np.median(e) < 0.06, f"{where}: half of the rows are off by more than {np.median(e):.3e} of the request's logit scale"
+    assert (e > 0.25).mean() <= 0.3, f"{where}: {int((e > 0.25).sum())} of {len(e)} rows are far off"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_schedules_agree_with_plain(models, plain, tmp_path, name, dtype):
+    reqs, want = plain[name]
+    vocab = ALL[name][0]["vocab"]
+    steps = traces.number(traces.whole(reqs) + traces.decode_tail(reqs) + traces.portions(reqs, 3))
+    got = traces.run_trace(models[name], dtype, steps, max_tokens=512, out_dir=str(tmp_path / "o"), vocab=vocab,
+                           page_size=PAGE_SIZE[name])
+    for tag in "wdp":
+        for k, toks in reqs.items():
+            check(rows_of(got, tag, k, len(toks)), want[k], dtype, f"{dtype} schedule '{tag}' request {k}")
+    if dtype == "float32":
+        for other in "dp":
+            for k, toks in reqs.items():
+                traces.check_same(rows_of(got, "w", k, len(toks)), rows_of(got, other, k, len(toks)), dtype,
+                                  f"{dtype} schedules 'w'/'{other}' request {k}", f32=5e-5)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_mixed_batches_in_a_small_pool(models, plain, tmp_path, name, dtype):
+    reqs, want = plain[name]
+    vocab = ALL[name][0]["vocab"]
+    longest = -(-max(len(t) for t in reqs.values()) // 64) * 64
+    max_tokens = longest + 128
+    steps = traces.number(traces.mixed(reqs, 5, max_tokens))
+    assert max(len(s["entries"]) for s in steps) >= 2
+    stats = {}
+    got = traces.run_trace(models[name], dtype, steps, max_tokens=max_tokens, out_dir=str(tmp_path / "o"), vocab=vocab,
+                           page_size=PAGE_SIZE[name], stats=stats)
+    for k, toks in reqs.items():
+        check(rows_of(got, "m", k, len(toks)), want[k], dtype, f"{dtype} mixed, request {k}")
+    assert stats["pages_reused"] > 0 and stats["slots_used"] == 0
+
+
+def run_cuts(r, toks, cuts_by_name):
+    out = {}
+    for rid, cut in cuts_by_name.items():
+        r.add_request(rid)
+        got, at = [], 0
+        for m in cut:
+            got.append(r.step([(rid, toks[at:at + m], list(range(m)))]).float().cpu().clone())
+            at += m
+        assert at == len(toks)
+        r.end_request(rid)
+        out[rid] = torch.cat(got).numpy()
+    return out
+
+
+def held(rows, want, dtype, where, sharp=2e-3):
+    if dtype == "float32":
+        assert np.abs(rows - want).max() < sharp, where
+    else:
+        traces.check_request(rows, want, dtype, where, bf16_row=0.35, bf16_mean=0.12)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sharp_window_edges_and_kept_first_positions(models, tmp_path, dtype):
+    from zig_ai_b200.engine.runner import load_runner
+    d = with_tensors(models["sharp_windowed"], str(tmp_path / "sharp"), lambda t: sharp_key(t, "l0.mix.", 10, 14))
+    cfg, tensors = read_model(d)
+    toks = tokens(cfg["vocab"], 150, 7)
+    want = P.forward(cfg, tensors, toks).numpy()
+    r = load_runner(d, dtype, max_tokens=256, max_requests=4, page_size=8)
+    got = run_cuts(r, toks, {"w": [150], "d": [5] + [1] * 145, "p": [3, 10, 2, 13, 1, 14, 2, 2, 13, 64, 26]})
+    for rid, rows in got.items():
+        held(rows, want, dtype, f"sharp window, cut {rid}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_far_keys_buckets_and_sink(models, tmp_path, dtype):
+    from zig_ai_b200.engine.runner import load_runner
+
+    def change(t):
+        sharp_key(t, "l0.mix.", 10, 14)
+        t["l0.mix.rel"] = (t["l0.mix.rel"].float() * 30.0).to(torch.bfloat16)
+        t["l0.mix.sink"] = (t["l0.mix.sink"].float() * 10.0 + 2.0).to(torch.bfloat16)
+    d = with_tensors(models["sharp_attention"], str(tmp_path / "far"), change)
+    cfg, tensors = read_model(d)
+    toks = tokens(cfg["vocab"], 400, 11)
+    want = P.forward(cfg, tensors, toks).numpy()
+    r = load_runner(d, dtype, max_tokens=512, max_requests=4, page_size=8)
+    got = run_cuts(r, toks, {"w": [400], "d": [340] + [1] * 60, "p": [8, 8, 7, 2, 15, 64, 1, 31, 14, 129, 121]})
+    for rid, rows in got.items():
+        held(rows, want, dtype, f"far keys, cut {rid}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_state_keeps_a_far_token(models, tmp_path, dtype):
+    from zig_ai_b200.engine.runner import load_runner
+
+    def change(t):
+        t["l0.mix.i.b"] = torch.full_like(t["l0.mix.i.b"], -6.0)
+        t["l0.mix.f.b"] = torch.full_like(t["l0.mix.f.b"], 8.0)
+        t["l0.mix.i"] = (t["l0.mix.i"].float() * 8.0).to(torch.bfloat16)
+    d = with_tensors(models["memory"], str(tmp_path / "mem"), change)
+    cfg, tensors = read_model(d)
+    toks = tokens(cfg["vocab"], 300, 13)
+    want = P.forward(cfg, tensors, toks).numpy()
+    r = load_runner(d, dtype, max_tokens=512, max_requests=4, page_size=8)
+    got = run_cuts(r, toks, {"w": [300], "d": [20] + [1] * 280, "p": [2, 2, 31, 16, 17, 2, 20, 128, 82]})
+    for rid, rows in got.items():
+        held(rows, want, dtype, f"far token in the state, cut {rid}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_through_the_graphs(models, dtype):
+    from zig_ai_b200.engine.runner import load_runner
+    name = "C"
+    cfg, tensors = read_model(models[name])
+    toks = tokens(cfg["vocab"], 330, 60)
+    want = P.forward(cfg, tensors, toks).numpy()
+    r = load_runner(models[name], dtype, max_tokens=512, max_requests=4, page_size=64)
+    r.add_request("l")
+    got = [r.step([("l", toks[:30], list(range(30)))]).float().cpu().clone()]
+    for t in toks[30:]:
+        got.append(r.step([("l", [t], [0])]).float().cpu().clone())
+    assert r.graphs is not None and r.graphs.replays >= 290
+    check(torch.cat(got).numpy(), want, dtype, f"{dtype} 300 decoded tokens")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_greedy_generation_through_the_entry_point(models, name, dtype):
+    import zig_ai_b200 as z
+    g = random.Random(3)
+    cfg, tensors = read_model(models[name])
+    prompts = [[g.randrange(cfg["vocab"]) for _ in range(n)] for n in (9, 21, 2, 40, 1)]
+    eng = z.Engine(models[name], dtype, max_num_seqs=4, max_batched_tokens=16, max_model_len=128, page_size=PAGE_SIZE[name])
+    outs = eng.generate(prompts, max_new_tokens=12, temperature=0.0)
+    for p, out in zip(prompts, outs):
+        assert len(out) == 12
+        if dtype == "bfloat16":
+            continue                 # a 16-bit router may send a token elsewhere: the choice is compared in 32-bit
+        logits = P.forward(cfg, tensors, p + out)
+        for i, tok in enumerate(out):
+            row = logits[len(p) + i - 1]
+            assert float(row.max() - row[tok]) <= 1e-3, f"{dtype}: token {i} of a request is not the plain implementation's choice"
+    assert eng.stats()["slots_used"] == 0
+
+
+def test_command_line_generates(models, tmp_path):
+    """The command line with a Lolivik model: random weights written from a config.json, and greedy tokens."""
+    cfg_path = tmp_path / "cfg.json"
+    cfg_path.write_text(json.dumps(ALL["A"][0]))
+    d = str(tmp_path / "m")
+    exe = [sys.executable, os.path.join(traces.ROOT, "bin", "zig-ai-engine")]
+    out = subprocess.run(exe + ["-m", d, "--prompt", "5,17,3,90,41", "-n", "10", "--dtype", "float32", "--page-size", "8",
+                                "--random-weights", str(cfg_path), "--seed", "7", "--temperature", "0"],
+                         capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert "Lolivik" in out.stdout
+    line = [ln for ln in out.stdout.splitlines() if ln.startswith("[0]")][0]
+    toks = [int(t) for t in line.split(")")[1].split()]
+    assert len(toks) == 10
+    cfg, tensors = read_model(d)
+    logits = P.forward(cfg, tensors, [5, 17, 3, 90, 41] + toks)
+    for i, tok in enumerate(toks):
+        row = logits[4 + i]
+        assert float(row.max() - row[tok]) < 1e-3
