@@ -250,6 +250,8 @@ def run_ours(args):
         return run_pikasun(args)
     if args.only == "zikevik":
         return run_zikevik(args)
+    if args.only == "lolivik":
+        return run_lolivik(args)
     if args.only == "long":
         return run_long(args)
     if args.only == "sample":
@@ -859,6 +861,194 @@ def run_zikevik(args):
     return 0
 
 
+def lolivik_config(width, layers=16, vocab=65536):
+    """A Lolivik model of a real model's proportions: groups of four layers (attention with shaped scores in front of a dense
+    gated feed-forward; a matrix memory in front of eight bounded experts of which a token uses two, with a shared unit;
+    windowed attention that keeps its first positions in front of the experts; a matrix memory in front of the dense
+    feed-forward).  Head size 64 (values too), four query heads a key/value head, a window of 1024, bias tables of 32 rows."""
+    heads = width // 64
+    dense = {"kind": "dense", "ff": 3 * width}
+    moe = {"kind": "moe", "expert": {"ff": width, "limit": 7.0}, "router": {"experts": 8, "top": 2}, "shared": {"ff": width, "limit": 7.0}}
+    att = {"heads": heads, "kv_heads": heads // 4, "dim": 64, "vdim": 64, "scale": 0.125, "softcap": 30.0, "bias_rows": 32,
+           "bias_max": 4096, "q_temp": {"coef": 0.1, "every": 1024}, "v_mix": True}
+    win = {"heads": heads, "kv_heads": heads // 4, "dim": 64, "vdim": 64, "scale": 0.125, "mask": {"size": 1024, "keep_first": 4},
+           "rot": {"base": 1e6, "dims": 32, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}, "v_mix": True}
+    mem = {"heads": heads // 2, "dim": 64, "vdim": 128, "gate_cap": 15.0}
+    group = [("attention", att, dense), ("mlstm", mem, moe), ("attention_2", win, moe), ("mlstm", mem, dense)]
+    return {"architecture": "Lolivik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.3,
+            "layers": [{"type": t, "mixer": dict(m), "mlp": dict(f)} for t, m, f in (group[i % 4] for i in range(layers))]}
+
+
+def lolivik_kernel_rooflines(width, hbm_peak, flops_peak):
+    """Every kernel that the design adds, alone at the sizes of `lolivik_config(width)`, beside the like kernel of an
+    existing design at the same sizes: attention with capped scores, a bias by distance and a sink, and windowed attention
+    with kept first positions, each beside plain grouped-query attention (LFM2's); the matrix memory beside the delta rule
+    with a decay per head (Vunolorn's, Zikevik's); the experts with softmax scores and bounded units beside those with
+    sigmoid scores and SiLU units (Zikevik's); the tanh-GELU gate beside the SiLU gate; the residual addition that rounds
+    the stream beside the one that norms it.  A portion of 2048 tokens and 64 single tokens over contexts of 2048, timed with
+    CUDA events, the L2 flushed before every call."""
+    import torch
+    from zig_ai_b200.cache.manager import CacheView
+    from zig_ai_b200.engine.batch import pack_step
+    from zig_ai_b200.kernels import ops
+    ops.require(torch.bfloat16, ("attention", "attention_mma", "attention_tma", "attention_tc", "qkv_prepare", "mlstm", "causal_conv",
+                                 "gated_delta", "moe", "gemm_tc"))
+    dev, dt = torch.device("cuda"), torch.bfloat16
+    H, G, D, ps = width // 64, width // 256, 64, 64
+    Hm, Dm, Vm = width // 128, 64, 128
+    E, top, F = 8, 2, width
+    g = torch.Generator().manual_seed(1)
+    rnd = lambda *shape, s=1.0: (torch.randn(*shape, generator=g) * s).to(dt).to(dev)
+    rows = []
+
+    def step_of(ctx, q_lens):
+        spans, tables, at = [], [], 1
+        width_pages = max(-(-(c + n) // ps) for c, n in zip(ctx, q_lens))
+        for s_, (c, n) in enumerate(zip(ctx, q_lens)):
+            need = -(-(c + n) // ps)
+            tables.append(list(range(at, at + need)) + [0] * (width_pages - need))
+            at += need
+            spans.append((s_, c, [0] * n, [], s_ + 1))
+        return pack_step(ops, dt, dev, spans, {0: tables}), at
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timed(fn, reps=10):
+        for _ in range(3):
+            fn()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        total = 0.0
+        for _ in range(reps):
+            flush.zero_()                                    # larger than L2: the timed call starts cold
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            total += a.elapsed_time(b)
+        return total / reps
+
+    for point, ctx, q_lens in (("2048-token portion", [0], [2048]), ("64 single tokens, context 2048", [2047] * 64, [1] * 64)):
+        step, n_pages = step_of(ctx, q_lens)
+        N, B = sum(q_lens), len(q_lens)
+        # attention: (query, key) pairs seen with and without the window
+        pairs = lambda w: sum(sum(min(c + i + 1, w) for i in range(n)) for c, n in zip(ctx, q_lens))
+        cached = sum(c + n for c, n in zip(ctx, q_lens))
+        view = CacheView(0, rnd(n_pages, 2, G, ps, D, s=0.5), step.block_tables[0], ps)
+        q = rnd(N, H * D)
+        bias, sink = (torch.randn(700, H, generator=g) * 0.5).to(dev), torch.zeros(H, device=dev)
+        by = cached * 2 * G * D * 2 + 2 * N * H * D * 2
+        full, win = 4.0 * pairs(1 << 30) * H * D, 4.0 * pairs(1024) * H * D
+        rows.append(("attention: capped scores, bias by distance, sink", point,
+                     timed(lambda: ops.paged_attention(q, step, view, H, G, D, 0.125, softcap=30.0, bias=bias, sink=sink)), full, by))
+        rows.append(("grouped-query attention (LFM2's)", point, timed(lambda: ops.paged_attention(q, step, view, H, G, D, 0.125)), full, by))
+        rows.append(("windowed attention, first positions kept", point,
+                     timed(lambda: ops.paged_attention(q, step, view, H, G, D, 0.125, 1024, keep_first=4)), win, by))
+        rows.append(("windowed attention (LFM2's kernels)", point, timed(lambda: ops.paged_attention(q, step, view, H, G, D, 0.125, 1024)), win, by))
+        # the matrix memory beside the delta rule at the same heads and sizes
+        at, cols = [], 0
+        for n in (Hm * Dm, Hm * Dm, Hm * Vm, Hm * Vm, Hm, Hm):
+            at.append(cols)
+            cols += -(-n // 8) * 8
+        y = rnd(N, cols)
+        zeros_h, nw = torch.zeros(Hm, device=dev), torch.ones(Hm * Vm, device=dev)
+        state = torch.zeros(B + 1, Hm, Dm + 1, Vm + 1, device=dev)
+        by = N * (cols + Hm * Vm) * 2 + B * Hm * Dm * Vm * 8
+        rows.append(("matrix memory with log gates", point,
+                     timed(lambda: ops.mlstm(y, at, zeros_h, zeros_h, 15.0, nw, 1e-6, state, step, Hm, Dm, Vm)), 0.0, by))
+        qkv, gate, b_, a_hd = rnd(N, 2 * Hm * Dm + Hm * Vm), rnd(N, Hm * Vm), rnd(N, Hm), rnd(N, Hm)
+        dstate = torch.zeros(B + 1, Hm, Dm, Vm, device=dev)
+        rows.append(("delta rule, a decay per head (Vunolorn's)", point,
+                     timed(lambda: ops.gated_delta(qkv, b_, a_hd, gate, zeros_h, zeros_h, torch.ones(Vm, device=dev), 1e-6, dstate, step,
+                                                   Hm, Hm, Dm, Vm)), 0.0, by))
+        # the feed-forwards
+        x = rnd(N, width)
+        w_router = (torch.randn(E, width, generator=g) * 0.05).to(dev)
+        w_gu, w_dn = rnd(E, 2 * F, width, s=0.02), rnd(E, width, F, s=0.02)
+        used = min(E, N * top)
+        fl, by = 2.0 * N * top * 3 * width * F, used * 3 * width * F * 2 + N * width * 4
+        rows.append((f"routed experts, softmax scores, bounded units ({top} of {E})", point,
+                     timed(lambda: ops.routed_experts(x, w_router, w_gu, w_dn, top, True, "output", score="softmax", act="clamped",
+                                                      limit=7.0, alpha=1.702)), fl, by))
+        rows.append((f"routed experts, sigmoid scores, SiLU units (Zikevik's)", point,
+                     timed(lambda: ops.routed_experts(x, w_router, w_gu, w_dn, top)), fl, by))
+        d_gu, d_dn = rnd(2 * 3 * width, width, s=0.02), rnd(width, 3 * width, s=0.02)
+        fl, by = 2.0 * N * 3 * width * 3 * width, 3 * width * 3 * width * 2 + N * width * 4
+        rows.append(("dense gated feed-forward, tanh GELU", point,
+                     timed(lambda: ops.linear(ops.linear_glu(x, d_gu, 3 * width, "gelu_tanh"), d_dn)), fl, by))
+        rows.append(("dense gated feed-forward, SiLU (LFM2's)", point,
+                     timed(lambda: ops.linear(ops.linear_swiglu(x, d_gu, 3 * width), d_dn)), fl, by))
+        # the residual addition
+        h, delta_ = torch.randn(N, width, generator=g).to(dev), rnd(N, width)
+        w1 = torch.ones(width, device=dev)
+        rows.append(("residual + normed term, stream rounded", point, timed(lambda: ops.add_cast(h, delta_, dt, w1, 1e-6)), 0.0, N * width * 12))
+        rows.append(("RMS norm + residual (shared with LFM2)", point, timed(lambda: ops.add_rmsnorm(h, delta_, w1, 1e-6, dt)), 0.0, N * width * 12))
+    return [{"kernel": k, "point": p, "width": width, "us": round(ms * 1e3, 2), "GFLOP": round(fl / 1e9, 2), "MB": round(by / 1e6, 2),
+             "TFLOP_per_s": round(fl / ms / 1e9, 1), "of_tensor_peak": round(fl / ms / 1e9 / flops_peak, 4),
+             "GB_per_s": round(by / ms / 1e6, 1), "of_copy_peak": round(by / ms / 1e6 / hbm_peak, 4)} for k, p, ms, fl, by in rows]
+
+
+def run_lolivik(args):
+    """Prefill and decode throughput of the Lolivik design at two widths beside the Zikevik design (the closest one: a
+    recurrent mixer and attention with a sink in front of dense feed-forwards and routed experts) of the same width, layer
+    count and vocabulary; the time of a prefill and of a decode step by kernel class; and its kernels alone beside the like
+    kernels.  JSON lines, then markdown."""
+    import torch
+    import zig_ai_b200 as z
+    from zig_ai_b200.config import config_from_dict
+    hbm_peak, flops_peak, peak_src = peaks()
+    rows, classes, kernels = [], [], []
+    for width in (1024, 2048):
+        for label, cfg_dict in ((f"Lolivik-{width}", lolivik_config(width)), (f"Zikevik-{width}", zikevik_config(width))):
+            cfg = config_from_dict(cfg_dict)
+            with tempfile.TemporaryDirectory(prefix="bench_lolivik_") as d:
+                z.write_random_model(cfg, 0, d)
+                eng = z.Engine(d, "bfloat16", max_num_seqs=64, max_batched_tokens=2048 + 64, max_model_len=CONTEXT,
+                               max_tokens=64 * CONTEXT, page_size=args.page_size)
+                nums = engine_numbers(eng)
+                active = params_read(nums, 1)
+                prefill_ms = time_prefill(eng, reps=5)
+                T = PREFILL_TOKENS
+                rows.append({"model": label, "width": width, "matrix_params_M": round(nums["matrix_params"] / 1e6, 1),
+                             "active_params_M": round(active / 1e6, 1), "point": "prefill 2048", "ms": round(prefill_ms, 3),
+                             "tokens_per_s": round(T / prefill_ms * 1e3),
+                             "matrix_TFLOP_per_s": round(2 * T * active / prefill_ms / 1e9, 1)})
+                print(json.dumps(rows[-1]), flush=True)
+                for B in (1, 8, 64):
+                    dev_ms, e2e_ms, ctx_tokens, launches, _, _, _ = time_decode(eng, B, max(min(args.steps, 100), 20), args.warmup)
+                    read = params_read(nums, B)       # of the experts, a step reads those that its tokens chose
+                    step_bytes = 2 * read + ctx_tokens * nums["kv_bytes_per_token"] + 2 * B * nums["state_bytes"]
+                    rows.append({"model": label, "width": width, "point": f"decode batch {B}", "ms": round(dev_ms, 4),
+                                 "e2e_ms": round(e2e_ms, 4), "tokens_per_s": round(B / dev_ms * 1e3),
+                                 "e2e_tokens_per_s": round(B / e2e_ms * 1e3), "GB_a_step": round(step_bytes / 1e9, 3),
+                                 "frac_of_copy_peak": round(step_bytes / (dev_ms * 1e-3) / 1e9 / hbm_peak, 3),
+                                 "launches_per_step": round(launches)})
+                    print(json.dumps(rows[-1]), flush=True)
+                g = random.Random(5)
+                V = eng.config.vocab_size
+                eng.flush()
+                pre = kernel_classes(eng, [("kc", [g.randrange(V) for _ in range(T)], [T - 1])])
+                dec = kernel_classes(eng, [(f"kc{i}", [g.randrange(V)], [0]) for i in range(64)])
+                classes.append({"model": label, "prefill_2048_ms_by_class": pre, "decode_64_first_token_ms_by_class": dec})
+                print(json.dumps(classes[-1]), flush=True)
+                del eng
+                torch.cuda.empty_cache()
+        kernels += lolivik_kernel_rooflines(width, hbm_peak, flops_peak)
+    for r in kernels:
+        print(json.dumps(r), flush=True)
+    print(f"\npeaks ({peak_src}): {hbm_peak:.0f} GB/s copy bandwidth, {flops_peak:.0f} TFLOP/s bf16 product (burst)\n")
+    print("| model | point | ms a step (device) | tokens/s (device) | tokens/s (end to end) | of the copy peak | launches a step |")
+    print("|---|---|---|---|---|---|---|")
+    for r in rows:
+        print(f"| {r['model']} | {r['point']} | {r['ms']} | {r['tokens_per_s']} | {r.get('e2e_tokens_per_s', '')} | "
+              f"{r.get('frac_of_copy_peak', '')} | {r.get('launches_per_step', '')} |")
+    print("\n| kernel | point | width | us | GFLOP | TFLOP/s | of the tensor peak | MB | GB/s | of the copy peak |")
+    print("|---|---|---|---|---|---|---|---|---|---|")
+    for r in kernels:
+        print(f"| {r['kernel']} | {r['point']} | {r['width']} | {r['us']} | {r['GFLOP']} | {r['TFLOP_per_s']} | {r['of_tensor_peak']} | "
+              f"{r['MB']} | {r['GB_per_s']} | {r['of_copy_peak']} |")
+    return 0
+
+
 def run_table(args):
     """The tracked table: the 350M, 700M and 1.2B shapes, decode at batch 1/8/64 device-timed and end to end,
     the prefill of 2048 tokens, and the mixed workload of the 700M shape, as JSON lines and as markdown."""
@@ -1212,9 +1402,9 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "gemm", "timeline", "table", "stream", "long", "sample", "vunolorn", "pikasun", "zikevik"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "gemm", "timeline", "table", "stream", "long", "sample", "vunolorn", "pikasun", "zikevik", "lolivik"],
                     help="profiling aid: run only the batch-8 decode steps or only the prefill (prints a short line); "
-                         "table: every figure of the 350M, 700M and 1.2B shapes (profiles/measurements.md); pikasun: the Pikasun design beside LFM2 at equal width; zikevik: the Zikevik design beside Pikasun at equal width, and its kernels beside the like ones; vunolorn: the "
+                         "table: every figure of the 350M, 700M and 1.2B shapes (profiles/measurements.md); pikasun: the Pikasun design beside LFM2 at equal width; zikevik: the Zikevik design beside Pikasun at equal width, and its kernels beside the like ones; lolivik: the Lolivik design beside Zikevik at equal width, and its kernels beside the like ones; vunolorn: the "
                          "Vunolorn hybrid at two widths beside LFM2 at equal width, and its recurrent kernels alone")
     ap.add_argument("--batch", type=int, default=8, help="with --only decode: the batch size; with --only stream: 24, 64 or "
                                                          "128 runs that row count only")

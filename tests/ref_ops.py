@@ -629,20 +629,22 @@ def linear_glu(x, w_gate_up, ff_dim, kind):
     return act_mul(linear(x, w_gate_up), ff_dim, kind)
 
 
-def mlstm(y, at, bias_i, bias_f, cap, norm_w, eps, state, step, heads, dim, vdim, write_state=True):
+def mlstm(y, at, bias_i, bias_f, cap, norm_w, eps, state, step, heads, dim, vdim, write_state=True, precision=torch.float32):
     """The matrix memory with log gates over the stacked projections y (columns `at`: q, k, v, output gate, the two log
     gates' inputs); state [slots, H, D + 1, Dv + 1]: S with the normaliser as its last column, the running maximum of
-    every column in the last row."""
+    every column in the last row.  `precision`: the type the recurrence is computed in (64-bit: the exact answer for a
+    32-bit kernel's test)."""
+    _f = lambda t: t.to(precision)
     N, H, D, Dv = y.shape[0], heads, dim, vdim
     q_at, k_at, v_at, g_at, i_at, f_at = at
     q = _f(y[:, q_at:q_at + H * D]).reshape(N, H, D) * D ** -0.5
     k = _f(y[:, k_at:k_at + H * D]).reshape(N, H, D)
-    v = torch.cat([_f(y[:, v_at:v_at + H * Dv]).reshape(N, H, Dv), torch.ones(N, H, 1, device=y.device)], dim=-1)
-    gi = cap * torch.tanh((_f(y[:, i_at:i_at + H]) + bias_i) / cap)
-    gf = torch.nn.functional.logsigmoid(cap * torch.tanh((_f(y[:, f_at:f_at + H]) + bias_f) / cap))
-    out = torch.zeros((N, H, Dv), dtype=torch.float32, device=y.device)
+    v = torch.cat([_f(y[:, v_at:v_at + H * Dv]).reshape(N, H, Dv), torch.ones(N, H, 1, device=y.device, dtype=precision)], dim=-1)
+    gi = cap * torch.tanh((_f(y[:, i_at:i_at + H]) + _f(bias_i)) / cap)
+    gf = torch.nn.functional.logsigmoid(cap * torch.tanh((_f(y[:, f_at:f_at + H]) + _f(bias_f)) / cap))
+    out = torch.zeros((N, H, Dv), dtype=precision, device=y.device)
     for a, b, slot in _spans(step, state):
-        S, m = state[slot][:, :D, :].clone(), state[slot][:, D, 0].clone()
+        S, m = _f(state[slot][:, :D, :]).clone(), _f(state[slot][:, D, 0]).clone()
         for t in range(a, b):
             new = torch.maximum(gf[t] + m, gi[t])
             keep, take = torch.exp(gf[t] + m - new), torch.exp(gi[t] - new)
@@ -651,8 +653,8 @@ def mlstm(y, at, bias_i, bias_f, cap, norm_w, eps, state, step, heads, dim, vdim
             r = torch.einsum("hdc,hd->hc", S, q[t])
             out[t] = r[:, :Dv] / (torch.maximum(r[:, Dv].abs(), torch.exp(-m)) + 1e-6)[:, None]
         if write_state:
-            state[slot][:, :D, :] = S
-            state[slot][:, D, :] = m[:, None]
+            state[slot][:, :D, :] = S.to(state.dtype)
+            state[slot][:, D, :] = m[:, None].to(state.dtype)
     o = out * torch.rsqrt((out * out).mean(-1, keepdim=True) + eps)
     g = torch.sigmoid(_f(y[:, g_at:g_at + H * Dv]))
-    return (o.reshape(N, H * Dv) * norm_w * g).to(y.dtype)
+    return (o.reshape(N, H * Dv) * _f(norm_w) * g).to(y.dtype)

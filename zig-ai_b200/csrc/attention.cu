@@ -21,13 +21,6 @@
 //   keep_first  with a window: the first keep_first positions of the request stay visible (at their true positions)
 #include "common.cuh"
 
-struct ZaiScoreOptions {
-    float softcap;
-    const float* bias;
-    int bias_rows;
-    const float* sink;
-    int keep_first;
-};
 
 template <typename T, int MAXR, bool EXT>
 __global__ void paged_attention_warp_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ pages,
@@ -114,7 +107,7 @@ ZAI_API int zai_paged_attention_general(void* out, const void* q, const void* pa
                                         int table_width, const int* positions, const int* seq_idx, int page_size,
                                         int N, int Hq, int Hkv, int D, float scale, int window, int num_pages, int* status,
                                         cudaStream_t stream) {
-    const ZaiScoreOptions opt = {0.f, nullptr, 0, nullptr, 0};
+    const ZaiScoreOptions opt = {0.f, nullptr, 0, nullptr, 0, 1.f};
     if (N <= 0) return ZAI_OK;
     if (D < 1 || D > 512 || Hkv < 1 || Hq % Hkv != 0 || Hq > 65535) return ZAI_BAD_SIZE;
     const dim3 grid(N, Hq);
@@ -142,7 +135,7 @@ ZAI_API int zai_paged_attention_scored(void* out, const void* q, const void* pag
                                         float softcap, const float* bias, int bias_rows, const float* sink, int keep_first,
                                         cudaStream_t stream) {
     if (softcap < 0.f || (bias && bias_rows < 1) || keep_first < 0 || (keep_first && window <= 0)) return ZAI_BAD_SIZE;
-    const ZaiScoreOptions opt = {softcap, bias, bias_rows, sink, keep_first};
+    const ZaiScoreOptions opt = {softcap, bias, bias_rows, sink, keep_first, scale};
     if (N <= 0) return ZAI_OK;
     if (D < 1 || D > 512 || Hkv < 1 || Hq % Hkv != 0 || Hq > 65535) return ZAI_BAD_SIZE;
     const dim3 grid(N, Hq);

@@ -121,12 +121,14 @@ __device__ __forceinline__ void pv_16keys(float (&o)[D / 8][4], const uint32_t (
 #define PREFILL_WARPS 8
 #define PREFILL_ROWS (16 * PREFILL_WARPS)      // query rows per block
 
-template <int D>
+// SHAPED: the scores pass `zai_shaped_score` (scale_log2 is then log2(e) alone), the sink joins the sums at the end, and
+// under a window the tiles of the kept first positions are walked before the window's.
+template <int D, bool SHAPED>
 __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_mma_kernel(
     bf16* __restrict__ out, const bf16* __restrict__ q, const bf16* __restrict__ pages,
     const int* __restrict__ block_table, int table_width, const int* __restrict__ cu_q,
     const int* __restrict__ ctx_lens, int S, int page_size, int Hq, int Hkv, float scale_log2, int window,
-    int num_pages, int* __restrict__ status) {
+    int num_pages, int* __restrict__ status, const ZaiScoreOptions opt) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int ST = D + 8, NT = PREFILL_WARPS * 32, QR = PREFILL_ROWS;
     bf16* sq = reinterpret_cast<bf16*>(smem_raw);           // [QR][ST]
@@ -161,6 +163,13 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_mma_kernel(
     const int kend = ctx + i0 + rows;                       // one past the last visible key of the block
     const int kbeg = zai_first_visible(ctx + i0, window);
     const int tile0 = kbeg / TILE, tile1 = (kend + TILE - 1) / TILE;
+    // kept first positions: their tiles below the window's first tile come first in the walk; rows of the window's
+    // first tile that lie before the window are loaded too when some of them are kept
+    const int keep = SHAPED && window > 0 ? opt.keep_first : 0;
+    const int kept_tiles = min((min(keep, kbeg) + TILE - 1) / TILE, tile0);
+    const int n_walk = kept_tiles + (tile1 - tile0);
+    const int load_lo = keep > 0 ? 0 : kbeg;
+    auto tile_at = [&](int n) { return n < kept_tiles ? n : tile0 + (n - kept_tiles); };
 
     // queries of the block: rows beyond the span are zeros
     for (int idx = tid; idx < QR * (D / 8); idx += NT) {
@@ -169,8 +178,8 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_mma_kernel(
         const bf16* src = valid ? q + ((size_t)(row0 + i0 + r) * Hq + h) * D + c * 8 : q;
         cp_async16(sq + r * ST + c * 8, src, valid);
     }
-    load_kv_tile<D, NT>(sk, pages, table, tile0 * TILE, kbeg, kend, page_size, page_shift, page_stride, k_off, tid);
-    load_kv_tile<D, NT>(sv, pages, table, tile0 * TILE, kbeg, kend, page_size, page_shift, page_stride, v_off, tid);
+    load_kv_tile<D, NT>(sk, pages, table, tile_at(0) * TILE, load_lo, kend, page_size, page_shift, page_stride, k_off, tid);
+    load_kv_tile<D, NT>(sv, pages, table, tile_at(0) * TILE, load_lo, kend, page_size, page_shift, page_stride, v_off, tid);
     cp_async_commit();
 
     uint32_t qf[D / 16][4];
@@ -183,12 +192,13 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_mma_kernel(
     const int lo0 = zai_first_visible(p0, window), lo1 = zai_first_visible(p1, window);
     const bool warp_has_rows = warp * 16 < rows;
 
-    for (int t = tile0; t < tile1; ++t) {
-        const int buf = (t - tile0) & 1;
-        if (t + 1 < tile1) {
-            load_kv_tile<D, NT>(sk + (buf ^ 1) * TILE * ST, pages, table, (t + 1) * TILE, kbeg, kend, page_size,
+    for (int n = 0; n < n_walk; ++n) {
+        const int t = tile_at(n);
+        const int buf = n & 1;
+        if (n + 1 < n_walk) {
+            load_kv_tile<D, NT>(sk + (buf ^ 1) * TILE * ST, pages, table, tile_at(n + 1) * TILE, load_lo, kend, page_size,
                                 page_shift, page_stride, k_off, tid);
-            load_kv_tile<D, NT>(sv + (buf ^ 1) * TILE * ST, pages, table, (t + 1) * TILE, kbeg, kend, page_size,
+            load_kv_tile<D, NT>(sv + (buf ^ 1) * TILE * ST, pages, table, tile_at(n + 1) * TILE, load_lo, kend, page_size,
                                 page_shift, page_stride, v_off, tid);
             cp_async_commit();
             cp_async_wait<1>();
@@ -196,7 +206,7 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_mma_kernel(
             cp_async_wait<0>();
         }
         __syncthreads();
-        if (t == tile0) {
+        if (n == 0) {
             const int r = warp * 16 + (((lane >> 3) & 1) << 3) + (lane & 7);
             const int dof = (lane >> 4) << 3;
 #pragma unroll
@@ -207,13 +217,24 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_mma_kernel(
         // a warp whose rows all lie before this tile's first key, or that has no rows, skips the tile
         const int warp_last_pos = ctx + i0 + warp * 16 + 15;
         const int warp_first_lo = zai_first_visible(ctx + i0 + warp * 16, window);
-        if (warp_has_rows && t * TILE <= warp_last_pos && (t + 1) * TILE > warp_first_lo) {
+        if (warp_has_rows && t * TILE <= warp_last_pos && ((t + 1) * TILE > warp_first_lo || t * TILE < keep)) {
             float sc[8][4];
 #pragma unroll
             for (int i = 0; i < 8; ++i) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
 #pragma unroll
             for (int kb = 0; kb < 4; ++kb) qk_16keys<D>(sc[2 * kb], sc[2 * kb + 1], qf, kt + kb * 16 * ST, lane);
             float mx0 = -INFINITY, mx1 = -INFINITY;
+            if (SHAPED) {
+#pragma unroll
+                for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int j = t * TILE + nt * 8 + 2 * tq + e;
+                        sc[nt][e] = zai_shaped_score(sc[nt][e], opt, p0, j, h, Hq);
+                        sc[nt][2 + e] = zai_shaped_score(sc[nt][2 + e], opt, p1, j, h, Hq);
+                    }
+                }
+            }
             const bool diag = (t + 1) * TILE - 1 > ctx + i0 + warp * 16 || window != 0;   // some element may be masked
             if (diag) {
 #pragma unroll
@@ -221,8 +242,8 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_mma_kernel(
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const int j = t * TILE + nt * 8 + 2 * tq + e;
-                        if (j > p0 || j < lo0) sc[nt][e] = -INFINITY;
-                        if (j > p1 || j < lo1) sc[nt][2 + e] = -INFINITY;
+                        if (j > p0 || (j < lo0 && j >= keep)) sc[nt][e] = -INFINITY;
+                        if (j > p1 || (j < lo1 && j >= keep)) sc[nt][2 + e] = -INFINITY;
                     }
                 }
             }
@@ -273,7 +294,14 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_mma_kernel(
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     const int r0 = warp * 16 + g, r1 = r0 + 8;
-    const float inv0 = 1.f / l0, inv1 = 1.f / l1;
+    float inv0 = 1.f / l0, inv1 = 1.f / l1;
+    if (SHAPED && opt.sink) {                               // the sink: a term of the denominator alone
+        const float sk = opt.sink[h];
+        const float n0 = fmaxf(m0, sk), n1 = fmaxf(m1, sk);
+        const float c0 = fast_exp2((m0 - n0) * scale_log2), c1 = fast_exp2((m1 - n1) * scale_log2);
+        inv0 = c0 / (l0 * c0 + fast_exp2((sk - n0) * scale_log2));
+        inv1 = c1 / (l1 * c1 + fast_exp2((sk - n1) * scale_log2));
+    }
 #pragma unroll
     for (int i = 0; i < D / 8; ++i) {
         const int d = i * 8 + 2 * tq;
@@ -289,12 +317,14 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_mma_kernel(
 // units, already scaled) and sum.  A chunk with no visible key writes (-inf, 0).
 template <int D> struct DecodeStages { static constexpr int N = ZAI_DECODE_STAGES; };   // tiles in flight + 1
 
-template <int D>
+// SHAPED: the scores pass `zai_shaped_score` (scale_log2 is then log2(e) alone); under a window the chunks that hold kept
+// first positions work too; the sink joins in the combine kernel.
+template <int D, bool SHAPED>
 __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
     float* __restrict__ part_o, float* __restrict__ part_ml, const bf16* __restrict__ q,
     const bf16* __restrict__ pages, const int* __restrict__ block_table, int table_width,
     const int* __restrict__ positions, int page_size, int Hq, int Hkv, float scale_log2, int window,
-    int num_pages, int* __restrict__ status) {
+    int num_pages, int* __restrict__ status, const ZaiScoreOptions opt) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int ST = D + 8, NS = DecodeStages<D>::N;
     bf16* sq = reinterpret_cast<bf16*>(smem_raw);           // [16][ST]
@@ -309,8 +339,9 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
     const int pos = positions[b];
     const int kend = pos + 1;
     const int kstart = zai_first_visible(pos, window);
-    const int lo = max(chunk * CHUNK, kstart), hi = min((chunk + 1) * CHUNK, kend);
-    if (lo >= hi) {
+    const int keep = SHAPED && window > 0 ? min(opt.keep_first, kstart) : 0;     // kept positions below the window
+    const int lo = chunk * CHUNK < keep ? chunk * CHUNK : max(chunk * CHUNK, kstart), hi = min((chunk + 1) * CHUNK, kend);
+    if (lo >= hi || (lo >= keep && hi <= kstart)) {
         if (tid < G) {
             float* ml = part_ml + (((size_t)b * Hq + hk * G + tid) * n_chunks + chunk) * 2;
             ml[0] = -INFINITY;
@@ -366,15 +397,22 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
             for (int ks = 0; ks < D / 16; ++ks) ldmatrix_x4(qf[ks], sq + r * ST + ks * 16 + dof);
         }
         const int j0 = t * TILE + warp * 16;                // this warp's 16 keys of the tile
-        if (j0 < hi && j0 + 16 > lo) {
+        if (j0 < hi && j0 + 16 > lo && (!SHAPED || j0 < keep || j0 + 16 > kstart)) {
             float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
             qk_16keys<D>(s0, s1, qf, sk + (buf * TILE + warp * 16) * ST, lane);
             float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int ja = j0 + 2 * tq + e, jb = ja + 8;
-                if (ja < lo || ja >= hi) { s0[e] = -INFINITY; s0[2 + e] = -INFINITY; }
-                if (jb < lo || jb >= hi) { s1[e] = -INFINITY; s1[2 + e] = -INFINITY; }
+                if (SHAPED) {                                   // rows g and g + 8 are query heads hk G + g and + 8
+                    const int ha = min(hk * G + g, Hq - 1), hb = min(hk * G + g + 8, Hq - 1);
+                    s0[e] = zai_shaped_score(s0[e], opt, pos, ja, ha, Hq);
+                    s0[2 + e] = zai_shaped_score(s0[2 + e], opt, pos, ja, hb, Hq);
+                    s1[e] = zai_shaped_score(s1[e], opt, pos, jb, ha, Hq);
+                    s1[2 + e] = zai_shaped_score(s1[2 + e], opt, pos, jb, hb, Hq);
+                }
+                if (ja < lo || ja >= hi || (SHAPED && ja >= keep && ja < kstart)) { s0[e] = -INFINITY; s0[2 + e] = -INFINITY; }
+                if (jb < lo || jb >= hi || (SHAPED && jb >= keep && jb < kstart)) { s1[e] = -INFINITY; s1[2 + e] = -INFINITY; }
                 mx0 = fmaxf(mx0, fmaxf(s0[e], s1[e]));
                 mx1 = fmaxf(mx1, fmaxf(s0[2 + e], s1[2 + e]));
             }
@@ -384,6 +422,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
             mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
             const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);   // finite: the warp has a visible key
             const float u0 = n0 * scale_log2, u1 = n1 * scale_log2;
+            if (SHAPED && n0 == -INFINITY) continue;            // (all 16 keys between the kept positions and the window)
             const float c0 = fast_exp2(m0 * scale_log2 - u0), c1 = fast_exp2(m1 * scale_log2 - u1);
             m0 = n0;
             m1 = n1;
@@ -453,15 +492,18 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
     }
 }
 
+// `sink` (or null): per head, a term exp(sink) of the denominator alone; the maxima are in log2 units.
 template <int D>
 __global__ void decode_combine_kernel(bf16* __restrict__ out, const float* __restrict__ part_o,
-                                      const float* __restrict__ part_ml, int n_chunks) {
+                                      const float* __restrict__ part_ml, int n_chunks, const float* __restrict__ sink, int Hq) {
     pdl_trigger();
     pdl_wait();
     const size_t bh = blockIdx.x;                           // b * Hq + h
     const float* ml = part_ml + bh * n_chunks * 2;
     float M = -INFINITY;
     for (int c = 0; c < n_chunks; ++c) M = fmaxf(M, ml[2 * c]);
+    const float sink2 = sink ? sink[bh % Hq] * 1.4426950408889634f : -INFINITY;
+    M = fmaxf(M, sink2);
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float acc = 0.f, L = 0.f;
         for (int c = 0; c < n_chunks; ++c) {
@@ -471,6 +513,7 @@ __global__ void decode_combine_kernel(bf16* __restrict__ out, const float* __res
             acc += part_o[(bh * n_chunks + c) * D + d] * f;
             L += ml[2 * c + 1] * f;
         }
+        if (sink) L += fast_exp2(sink2 - M);
         out[bh * D + d] = __float2bfloat16_rn(acc / L);
     }
 }
@@ -770,35 +813,51 @@ template <int D> size_t decode_smem() {
 template <int D>
 static int launch_prefill(bf16* out, const bf16* q, const bf16* pages, const int* block_table, int table_width,
                           const int* cu_q, const int* ctx_lens, int S, int n_tiles, int page_size, int Hq, int Hkv,
-                          float scale, int window, int num_pages, int* status, cudaStream_t stream) {
+                          float scale, int window, int num_pages, int* status, cudaStream_t stream,
+                          const ZaiScoreOptions* shaped = nullptr) {
     const size_t smem = prefill_smem<D>();
     static unsigned long long configured = 0;
     if (zai_first_on_device(&configured)) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(prefill_mma_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_mma_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    return launch_pdl(prefill_mma_kernel<D>, dim3(n_tiles, Hq), dim3(PREFILL_WARPS * 32), smem, stream,
+    if (shaped)
+        return launch_pdl(prefill_mma_kernel<D, true>, dim3(n_tiles, Hq), dim3(PREFILL_WARPS * 32), smem, stream,
+                          out, q, pages, block_table, table_width, cu_q, ctx_lens, S, page_size, Hq, Hkv,
+                          1.4426950408889634f, window, num_pages, status, *shaped);
+    const ZaiScoreOptions none = {0.f, nullptr, 0, nullptr, 0, 1.f};
+    return launch_pdl(prefill_mma_kernel<D, false>, dim3(n_tiles, Hq), dim3(PREFILL_WARPS * 32), smem, stream,
                       out, q, pages, block_table, table_width, cu_q, ctx_lens, S, page_size, Hq, Hkv,
-                      scale * 1.4426950408889634f, window, num_pages, status);
+                      scale * 1.4426950408889634f, window, num_pages, status, none);
 }
 
 template <int D>
 static int launch_decode(bf16* out, float* part_o, float* part_ml, const bf16* q, const bf16* pages,
                          const int* block_table, int table_width, const int* positions, int B, int n_chunks,
                          int page_size, int Hq, int Hkv, float scale, int window, int num_pages, int* status,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, const ZaiScoreOptions* shaped = nullptr) {
     const size_t smem = decode_smem<D>();
     static unsigned long long configured = 0;
     if (zai_first_on_device(&configured)) {
-        cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_mma_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    int e = launch_pdl(decode_mma_kernel<D>, dim3(n_chunks, Hkv, B), dim3(NTHREADS), smem, stream,
+    int e;
+    if (shaped) {
+        e = launch_pdl(decode_mma_kernel<D, true>, dim3(n_chunks, Hkv, B), dim3(NTHREADS), smem, stream,
                        part_o, part_ml, q, pages, block_table, table_width, positions, page_size, Hq, Hkv,
-                       scale * 1.4426950408889634f, window, num_pages, status);
+                       1.4426950408889634f, window, num_pages, status, *shaped);
+    } else {
+        const ZaiScoreOptions none = {0.f, nullptr, 0, nullptr, 0, 1.f};
+        e = launch_pdl(decode_mma_kernel<D, false>, dim3(n_chunks, Hkv, B), dim3(NTHREADS), smem, stream,
+                       part_o, part_ml, q, pages, block_table, table_width, positions, page_size, Hq, Hkv,
+                       scale * 1.4426950408889634f, window, num_pages, status, none);
+    }
     if (e) return e;
     return launch_pdl(decode_combine_kernel<D>, dim3(B * Hq), dim3(D <= 64 ? 64 : 128), 0, stream,
-                      out, (const float*)part_o, (const float*)part_ml, n_chunks);
+                      out, (const float*)part_o, (const float*)part_ml, n_chunks, shaped ? shaped->sink : (const float*)nullptr, Hq);
 }
 
 #define ZAI_HEAD_DIMS(X) X(16) X(32) X(48) X(64) X(80) X(96) X(128)
@@ -820,6 +879,43 @@ ZAI_API int zai_prefill_attention_mma(void* out, const void* q, const void* page
     if (Hq > 65535) return ZAI_BAD_SIZE;
 #define X(d) if (D == d) return launch_prefill<d>((bf16*)out, (const bf16*)q, (const bf16*)pages, block_table, table_width, \
                                                   cu_q, ctx_lens, S, n_tiles, page_size, Hq, Hkv, scale, window, num_pages, status, stream);
+    ZAI_HEAD_DIMS(X)
+#undef X
+    return ZAI_BAD_SIZE;
+}
+
+// The two kernels above with shaped scores: softcap (0: none), bias [bias_rows, Hq] by distance (or null), sink [Hq] (or
+// null), keep_first (with a window).
+static inline bool zai_shaped_ok(float softcap, const float* bias, int bias_rows, int keep_first, int window) {
+    return softcap >= 0.f && (!bias || bias_rows >= 1) && keep_first >= 0 && (!keep_first || window > 0);
+}
+
+ZAI_API int zai_prefill_attention_mma_scored(void* out, const void* q, const void* pages, const int* block_table,
+                                             int table_width, const int* cu_q, const int* ctx_lens, int S, int n_tiles,
+                                             int page_size, int Hq, int Hkv, int D, float scale, int window,
+                                             int num_pages, int* status, float softcap, const float* bias, int bias_rows,
+                                             const float* sink, int keep_first, cudaStream_t stream) {
+    if (S <= 0 || n_tiles <= 0) return ZAI_OK;
+    if (Hq > 65535 || !zai_shaped_ok(softcap, bias, bias_rows, keep_first, window)) return ZAI_BAD_SIZE;
+    const ZaiScoreOptions opt = {softcap, bias, bias_rows, sink, keep_first, scale};
+#define X(d) if (D == d) return launch_prefill<d>((bf16*)out, (const bf16*)q, (const bf16*)pages, block_table, table_width, \
+                                                  cu_q, ctx_lens, S, n_tiles, page_size, Hq, Hkv, scale, window, num_pages, status, stream, &opt);
+    ZAI_HEAD_DIMS(X)
+#undef X
+    return ZAI_BAD_SIZE;
+}
+
+ZAI_API int zai_decode_attention_mma_scored(void* out, float* part_o, float* part_ml, const void* q, const void* pages,
+                                            const int* block_table, int table_width, const int* positions, int B,
+                                            int n_chunks, int page_size, int Hq, int Hkv, int D, float scale, int window,
+                                            int num_pages, int* status, float softcap, const float* bias, int bias_rows,
+                                            const float* sink, int keep_first, cudaStream_t stream) {
+    if (B <= 0) return ZAI_OK;
+    if (n_chunks < 1 || Hkv < 1 || Hkv > 65535 || B > 65535 || Hq % Hkv != 0 || Hq / Hkv > 16
+        || !zai_shaped_ok(softcap, bias, bias_rows, keep_first, window)) return ZAI_BAD_SIZE;
+    const ZaiScoreOptions opt = {softcap, bias, bias_rows, sink, keep_first, scale};
+#define X(d) if (D == d) return launch_decode<d>((bf16*)out, part_o, part_ml, (const bf16*)q, (const bf16*)pages, block_table, \
+                                                 table_width, positions, B, n_chunks, page_size, Hq, Hkv, scale, window, num_pages, status, stream, &opt);
     ZAI_HEAD_DIMS(X)
 #undef X
     return ZAI_BAD_SIZE;

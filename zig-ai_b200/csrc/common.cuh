@@ -57,6 +57,28 @@ __host__ __device__ __forceinline__ int zai_first_visible(int pos, int window) {
     return 0;
 }
 
+// Options of attention kernels for designs that shape their scores (all off: zeros and null pointers):
+//   softcap     s <- cap * tanh(s / cap), after the scale and before anything is added
+//   bias        s <- s + bias[min(pos - j, bias_rows - 1), head]: a table by distance, added after the cap, not scaled
+//   sink        one more term exp(sink[head]) in the softmax's denominator, with no key and no value
+//   keep_first  with a window: the first keep_first positions of the request stay visible (at their true positions)
+//   scale       the factor on q . k (the tensor-core kernels, which otherwise fold it into their exponent)
+struct ZaiScoreOptions {
+    float softcap;
+    const float* bias;
+    int bias_rows;
+    const float* sink;
+    int keep_first;
+    float scale;
+};
+// A raw dot product to the shaped score of query position `pos`, key position j and query head h of Hq.
+__device__ __forceinline__ float zai_shaped_score(float dot, const ZaiScoreOptions& opt, int pos, int j, int h, int Hq) {
+    float s = dot * opt.scale;
+    if (opt.softcap > 0.f) s = opt.softcap * tanhf(s / opt.softcap);
+    if (opt.bias) s += opt.bias[(size_t)min(max(pos - j, 0), opt.bias_rows - 1) * Hq + h];
+    return s;
+}
+
 // ---- the status word of a step: one device int that kernels OR bits into and the host reads with the
 // step's results.  A kernel never traps and never touches memory outside the tensors it was given: an
 // id outside its bound is replaced by id 0 (page 0 and slot 0 are never handed to a request, padding

@@ -79,7 +79,7 @@ struct SkinnyArgs {
     int l2_prefetch_bytes; // how much of its weight rows a block asks into L2 before it waits for the kernel before it
     NextWeights next;      // the weights of the product after this one: asked into L2 while this one runs
     // gated epilogue with bounded branches (glu_limit > 0): g = min(gate, limit), u = clamp(up, -limit, limit),
-    // y = g * sigmoid(glu_slope * g) * (u + 1); glu_limit = 0: y = silu(gate) * up
+    // y = g * sigmoid(glu_slope * g) * (u + 1); glu_limit = 0: y = silu(gate) * up; glu_limit < 0: y = gelu_tanh(gate) * up
     float glu_limit, glu_slope;
     // layer norm instead of RMS norm (norm variants only): the row's mean is taken off before the squares are summed,
     // and beta_dot[o] = sum_k W[o, k] * beta[k] (the norm's bias through the product, made once per matrix) is added to
@@ -515,7 +515,10 @@ __global__ void __launch_bounds__(SG_WARPS * 32, 2) skinny_gemm_kernel(const Ski
                             up = fminf(fmaxf(hi, -a.glu_limit), a.glu_limit) + 1.f;
                             slope = a.glu_slope;
                         }
-                        reinterpret_cast<bf16*>(a.y)[(size_t)tok * a.ldy + row_lo] = __float2bfloat16_rn(gt / (1.f + expf(-slope * gt)) * up);
+                        const float act = a.glu_limit < 0.f          // (a negative limit: the gate passes the tanh form of GELU)
+                            ? 0.5f * lo * (1.f + tanhf(0.79788456080286536f * (lo + 0.044715f * lo * lo * lo)))
+                            : gt / (1.f + expf(-slope * gt));
+                        reinterpret_cast<bf16*>(a.y)[(size_t)tok * a.ldy + row_lo] = __float2bfloat16_rn(act * up);
                     }
                 } else if (EPI == EPI_F32) {
                     if (row_lo >= 0) reinterpret_cast<float*>(a.y)[(size_t)tok * a.ldy + row_lo] = lo;
@@ -934,7 +937,7 @@ ZAI_API int zai_skinny_gemm_layernorm(void* y, const void* W, const float* h, co
 ZAI_API int zai_skinny_gemm_clamped_glu(void* y, const void* W, const void* x, const float* h, const void* delta,
                                         const float* gamma, const int* row_idx, float* h_out, float eps, int M, int O, int K,
                                         float limit, float slope, cudaStream_t stream) {
-    if (!(limit > 0.f)) return ZAI_BAD_SIZE;
+    if (limit == 0.f) return ZAI_BAD_SIZE;               // (limit < 0: the tanh-GELU gate, see the kernel's arguments)
     return skinny_gemm_run(y, W, x, h, delta, gamma, row_idx, h_out, eps, M, O, K, EPI_SWIGLU, limit, slope, stream);
 }
 

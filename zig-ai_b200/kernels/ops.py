@@ -89,6 +89,9 @@ _SIGNATURES = {
         "zai_attention_mma_supports": [_I, _I, _I],
         "zai_prefill_attention_mma": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
         "zai_decode_attention_mma": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
+        "zai_prefill_attention_mma_scored": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _F, _P, _I, _P, _I, _P],
+        "zai_decode_attention_mma_scored": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _F, _P, _I, _P, _I,
+                                            _P],
         "zai_decode_attention_fused": [_P, _P, _P, _P, _P, _I, _P, _P, _F, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I,
                                        _F, _I, _I, _I, _I, _P, _P],
         "zai_decode_chunk_keys": [],
@@ -902,6 +905,27 @@ def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=Non
         if (cache.pages.dtype != q.dtype or N != step.n_tokens or (bias is not None and (bias.dtype != torch.float32 or bias.shape[1] != heads))
                 or (sink is not None and (sink.dtype != torch.float32 or sink.numel() != heads))):
             raise KernelError("paged_attention: operands do not fit together")
+        shaped = (float(softcap or 0.0), _ptr(bias), 0 if bias is None else bias.shape[0], _ptr(sink), int(keep_first or 0))
+        if (impl != "general" and q.dtype == torch.bfloat16 and q.is_contiguous()
+                and _fn("attention_mma", "zai_attention_mma_supports")(head_dim, heads, kv_heads)):
+            # the tensor-core kernels with the scores shaped inside them
+            if step.decode_only:
+                keys = _fn("attention_mma", "zai_decode_chunk_keys")()
+                n_chunks = max(-(-int(step.max_kv_len) // keys), 1)
+                part_o = torch.empty((N, heads, n_chunks, head_dim), dtype=torch.float32, device=q.device)
+                part_ml = torch.empty((N, heads, n_chunks, 2), dtype=torch.float32, device=q.device)
+                _check(_fn("attention_mma", "zai_decode_attention_mma_scored")(
+                    _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(q), _ptr(cache.pages), _ptr(bt), bt.shape[1], _ptr(step.positions), N,
+                    n_chunks, cache.page_size, heads, kv_heads, head_dim, float(scale), int(window or 0), cache.pages.shape[0],
+                    _status_ptr(q.device), *shaped, _stream()), "decode attention (scored)", 2)
+                return out
+            block_rows = _fn("attention_mma", "zai_prefill_block_rows")()
+            n_tiles = step.attn_tiles if getattr(step, "attn_tiles", None) else sum(-(-n // block_rows) for n in step.q_lens)
+            _check(_fn("attention_mma", "zai_prefill_attention_mma_scored")(
+                _ptr(out), _ptr(q), _ptr(cache.pages), _ptr(bt), bt.shape[1], _ptr(step.cu_q), _ptr(step.ctx_lens), step.n_seqs,
+                n_tiles, cache.page_size, heads, kv_heads, head_dim, float(scale), int(window or 0), cache.pages.shape[0],
+                _status_ptr(q.device), *shaped, _stream()), "prefill attention (scored)")
+            return out
         _check(_fn("attention", "zai_paged_attention_scored")(
             _ptr(out), _ptr(q), _ptr(cache.pages), _dt(q), _ptr(bt), bt.shape[1], _ptr(step.positions), _ptr(step.seq_idx),
             cache.page_size, N, heads, kv_heads, head_dim, float(scale), int(window or 0), cache.pages.shape[0],
@@ -1553,6 +1577,10 @@ def linear_glu(x, w_gate_up, ff_dim, kind):
     """The stacked gate|up product (x may be a LazyNorm) and act(gate) * up; SiLU takes the fused ways of `linear_swiglu`."""
     if kind == "silu":
         return linear_swiglu(x, w_gate_up, ff_dim)
+    if kind == "gelu_tanh" and x.dtype == torch.bfloat16:
+        y = _skinny(x, w_gate_up, _EPI_SWIGLU, ff_dim, torch.bfloat16, glu=(-1.0, 0.0))     # few rows: the product's epilogue
+        if y is not None:
+            return y
     return act_mul(linear(x, w_gate_up), ff_dim, kind)
 
 
