@@ -941,6 +941,9 @@ def lolivik_kernel_rooflines(width, hbm_peak, flops_peak):
         rows.append(("attention: capped scores, bias by distance, sink", point,
                      timed(lambda: ops.paged_attention(q, step, view, H, G, D, 0.125, softcap=30.0, bias=bias, sink=sink)), full, by))
         rows.append(("grouped-query attention (LFM2's)", point, timed(lambda: ops.paged_attention(q, step, view, H, G, D, 0.125)), full, by))
+        if N > B:       # (spans: the same work on the span kernel of the generation before, which is the one that shapes scores)
+            rows.append(("grouped-query attention, the mma.sync span kernel", point,
+                         timed(lambda: ops.paged_attention(q, step, view, H, G, D, 0.125, impl="mma")), full, by))
         rows.append(("windowed attention, first positions kept", point,
                      timed(lambda: ops.paged_attention(q, step, view, H, G, D, 0.125, 1024, keep_first=4)), win, by))
         rows.append(("windowed attention (LFM2's kernels)", point, timed(lambda: ops.paged_attention(q, step, view, H, G, D, 0.125, 1024)), win, by))

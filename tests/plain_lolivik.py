@@ -158,12 +158,17 @@ def bounded_unit(tensors, pre, h, limit, dt):
     return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ W("down").T
 
 
-def feed_forward(mlp, tensors, pre, h, dt):
+def feed_forward(mlp, tensors, pre, h, dt, margins_out=None):
+    """`margins_out`: a list that receives, for a mixture of experts, per token how far the last chosen score lies above the
+    first one left out, as a share of the former (where that is tiny, a lower precision may choose otherwise)."""
     W = lambda n: tensors[pre + n].to(dt)
     if mlp["kind"] == "dense":
         return (gelu_tanh(h @ W("gate").T) * (h @ W("up").T)) @ W("down").T
     E, top = mlp["router"]["experts"], mlp["router"]["top"]
     s = torch.softmax(h @ W("router").T, dim=-1)
+    if margins_out is not None and top < E:
+        ranked = s.sort(dim=-1, descending=True).values
+        margins_out.append((ranked[:, top - 1] - ranked[:, top]) / ranked[:, top - 1])
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         chosen = sorted(range(E), key=lambda e: (-float(s[t, e]), e))[:top]
@@ -175,7 +180,7 @@ def feed_forward(mlp, tensors, pre, h, dt):
     return out
 
 
-def forward(cfg, tensors, tokens, dt=torch.float64, layers_out=None):
+def forward(cfg, tensors, tokens, dt=torch.float64, layers_out=None, margins_out=None):
     eps, mult = cfg["norm"]["eps"], cfg["residual_mult"]
     x = tensors["embed"].to(dt)[torch.tensor(tokens, dtype=torch.long)]
     v_first = None
@@ -190,7 +195,7 @@ def forward(cfg, tensors, tokens, dt=torch.float64, layers_out=None):
                 v_first = v
         x = x + mult * rms(y, eps) * tensors[pre + "norm1"].to(dt)
         if layer["mlp"] is not None:
-            y = feed_forward(layer["mlp"], tensors, pre + "mlp.", x, dt)
+            y = feed_forward(layer["mlp"], tensors, pre + "mlp.", x, dt, margins_out)
             x = x + mult * rms(y, eps) * tensors[pre + "norm2"].to(dt)
         if layers_out is not None:
             layers_out.append(x.clone())

@@ -42,22 +42,41 @@ def plain(models):
     for name in ALL:
         cfg, tensors = read_model(models[name])
         reqs = traces.requests_for(cfg["vocab"], LENGTHS[name], 78)
-        out[name] = (reqs, {k: P.forward(cfg, tensors, t).numpy() for k, t in reqs.items()})
+        want, sure = {}, {}
+        for k, t in reqs.items():
+            want[k], sure[k] = plain_with_margins(cfg, tensors, t)
+        out[name] = (reqs, want, sure)
     return out
+
+
+def plain_with_margins(cfg, tensors, toks, close=1e-4):
+    """The plain logits, and how many rows from the start no router had a close call in: two scores around the cut that
+    differ by less than `close` of their size may be chosen the other way round in 32-bit, which is no fault, and what such
+    a row leaves in the caches and states moves the rows after it."""
+    margins = []
+    logits = P.forward(cfg, tensors, toks, margins_out=margins).numpy()
+    if not margins:
+        return logits, len(toks)
+    tight = (torch.stack(margins) < close).any(dim=0)
+    return logits, int(tight.nonzero()[0]) if bool(tight.any()) else len(toks)
 
 
 def rows_of(got, tag, k, n):
     return np.stack([got[(tag + k, p)] for p in range(n)])
 
 
-def check(got_rows, want_rows, dtype, where):
-    """32-bit: every row, strictly.  bfloat16: a 16-bit router may send a row to another expert than the 64-bit one where two
+def check(got_rows, want_rows, dtype, where, sure=None):
+    """32-bit: every row before the request's first close call of a router (`sure` rows; see `plain_with_margins`), strictly;
+    the rows from there on as in bfloat16.  bfloat16: a 16-bit router may send a row to another expert than the 64-bit one where two
     scores lie closer than the input's rounding, and what that row leaves in the cache and the state moves the rows after it;
     so half of the rows are held tightly and the share of rows that are far off is bounded.  The 32-bit run of the same
     schedule holds every row, through the same cache and batch code."""
+    sure = len(want_rows) if sure is None else sure
     if dtype == "float32":
-        traces.check_request(got_rows, want_rows, dtype, where)
-        return
+        if sure:
+            traces.check_request(got_rows[:sure], want_rows[:sure], dtype, where)
+        if sure == len(want_rows):
+            return
     e = traces.request_errors(got_rows, want_rows)
     assert np.median(e) < 0.06, f"{where}: half of the rows are off by more than {np.median(e):.3e} of the request's logit scale"
     assert (e > 0.25).mean() <= 0.3, f"{where}: {int((e > 0.25).sum())} of {len(e)} rows are far off"
@@ -66,25 +85,26 @@ def check(got_rows, want_rows, dtype, where):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_schedules_agree_with_plain(models, plain, tmp_path, name, dtype):
-    reqs, want = plain[name]
+    reqs, want, sure = plain[name]
     vocab = ALL[name][0]["vocab"]
     steps = traces.number(traces.whole(reqs) + traces.decode_tail(reqs) + traces.portions(reqs, 3))
     got = traces.run_trace(models[name], dtype, steps, max_tokens=512, out_dir=str(tmp_path / "o"), vocab=vocab,
                            page_size=PAGE_SIZE[name])
     for tag in "wdp":
         for k, toks in reqs.items():
-            check(rows_of(got, tag, k, len(toks)), want[k], dtype, f"{dtype} schedule '{tag}' request {k}")
+            check(rows_of(got, tag, k, len(toks)), want[k], dtype, f"{dtype} schedule '{tag}' request {k}", sure[k])
     if dtype == "float32":
         for other in "dp":
             for k, toks in reqs.items():
-                traces.check_same(rows_of(got, "w", k, len(toks)), rows_of(got, other, k, len(toks)), dtype,
-                                  f"{dtype} schedules 'w'/'{other}' request {k}", f32=5e-5)
+                if sure[k]:
+                    traces.check_same(rows_of(got, "w", k, len(toks))[:sure[k]], rows_of(got, other, k, len(toks))[:sure[k]], dtype,
+                                      f"{dtype} schedules 'w'/'{other}' request {k}", f32=5e-5)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_mixed_batches_in_a_small_pool(models, plain, tmp_path, name, dtype):
-    reqs, want = plain[name]
+    reqs, want, sure = plain[name]
     vocab = ALL[name][0]["vocab"]
     longest = -(-max(len(t) for t in reqs.values()) // 64) * 64
     max_tokens = longest + 128
@@ -94,7 +114,7 @@ def test_mixed_batches_in_a_small_pool(models, plain, tmp_path, name, dtype):
     got = traces.run_trace(models[name], dtype, steps, max_tokens=max_tokens, out_dir=str(tmp_path / "o"), vocab=vocab,
                            page_size=PAGE_SIZE[name], stats=stats)
     for k, toks in reqs.items():
-        check(rows_of(got, "m", k, len(toks)), want[k], dtype, f"{dtype} mixed, request {k}")
+        check(rows_of(got, "m", k, len(toks)), want[k], dtype, f"{dtype} mixed, request {k}", sure[k])
     assert stats["pages_reused"] > 0 and stats["slots_used"] == 0
 
 
@@ -174,14 +194,14 @@ def test_long_decoding_through_the_graphs(models, dtype):
     name = "C"
     cfg, tensors = read_model(models[name])
     toks = tokens(cfg["vocab"], 330, 60)
-    want = P.forward(cfg, tensors, toks).numpy()
+    want, sure = plain_with_margins(cfg, tensors, toks)
     r = load_runner(models[name], dtype, max_tokens=512, max_requests=4, page_size=64)
     r.add_request("l")
     got = [r.step([("l", toks[:30], list(range(30)))]).float().cpu().clone()]
     for t in toks[30:]:
         got.append(r.step([("l", [t], [0])]).float().cpu().clone())
     assert r.graphs is not None and r.graphs.replays >= 290
-    check(torch.cat(got).numpy(), want, dtype, f"{dtype} 300 decoded tokens")
+    check(torch.cat(got).numpy(), want, dtype, f"{dtype} 300 decoded tokens", sure)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

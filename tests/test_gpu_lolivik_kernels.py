@@ -215,8 +215,9 @@ def test_routed_experts_softmax_scores_bounded_units(dtype, N, W, F, E, top):
     kw = dict(score="softmax", act="clamped", limit=1.2, alpha=1.702)
     a = o.routed_experts(x, w_router, w_gate_up, w_down, top, True, "output", **kw)
     b = ref_ops.routed_experts(x, w_router, w_gate_up, w_down, top, True, "output", **kw)
-    s = torch.softmax(x.float() @ w_router.t(), dim=-1).sort(dim=-1, descending=True).values
-    sure = torch.ones(N, dtype=torch.bool, device="cuda") if top == E else (s[:, top - 1] - s[:, top]) > 1e-4
+    # a row whose scores around the cut lie closer together than the router's rounding may go to another expert in the two versions
+    z = (x.float() @ w_router.t()).sort(dim=-1, descending=True).values
+    sure = torch.ones(N, dtype=torch.bool, device="cuda") if top == E else (z[:, top - 1] - z[:, top]) > 1e-3
     assert int(sure.sum()) >= N - max(2, N // 100)
     assert torch.allclose(a.float()[sure], b.float()[sure], **tol(dtype))
     unbounded = ref_ops.routed_experts(x, w_router, w_gate_up, w_down, top, True, "output", score="softmax", act="clamped", limit=50.0)

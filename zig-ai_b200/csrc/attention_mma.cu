@@ -117,6 +117,18 @@ __device__ __forceinline__ void pv_16keys(float (&o)[D / 8][4], const uint32_t (
     }
 }
 
+// `zai_shaped_score` for these kernels: the cap's tanh as 1 - 2 / (1 + e^(2x)) with the approximate exponential and division
+// (an absolute error of a few 1e-6 of the cap, far below what the bfloat16 rounding of q and k leaves in a score).
+__device__ __forceinline__ float shaped_score_fast(float dot, const ZaiScoreOptions& opt, int pos, int j, int h, int Hq) {
+    float s = dot * opt.scale;
+    if (opt.softcap > 0.f) {
+        const float e = fast_exp2(s * __fdividef(2.8853900817779268f, opt.softcap));
+        s = opt.softcap * (1.f - __fdividef(2.f, 1.f + e));
+    }
+    if (opt.bias) s += __ldg(opt.bias + (size_t)min(max(pos - j, 0), opt.bias_rows - 1) * Hq + h);
+    return s;
+}
+
 // ------------------------------------------------------------------------------------------ prefill
 #define PREFILL_WARPS 8
 #define PREFILL_ROWS (16 * PREFILL_WARPS)      // query rows per block
@@ -225,13 +237,21 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_mma_kernel(
             for (int kb = 0; kb < 4; ++kb) qk_16keys<D>(sc[2 * kb], sc[2 * kb + 1], qf, kt + kb * 16 * ST, lane);
             float mx0 = -INFINITY, mx1 = -INFINITY;
             if (SHAPED) {
+                // a tile that lies beyond the bias table's last row for all of the warp's rows gets that row's value
+                // without a lookup (the table ends at the first distance of its last bucket: most tiles of a long context)
+                ZaiScoreOptions so = opt;
+                float far_bias = 0.f;
+                if (opt.bias && (ctx + i0 + warp * 16) - (t * TILE + TILE - 1) >= opt.bias_rows - 1) {
+                    far_bias = __ldg(opt.bias + (size_t)(opt.bias_rows - 1) * Hq + h);
+                    so.bias = nullptr;
+                }
 #pragma unroll
                 for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const int j = t * TILE + nt * 8 + 2 * tq + e;
-                        sc[nt][e] = zai_shaped_score(sc[nt][e], opt, p0, j, h, Hq);
-                        sc[nt][2 + e] = zai_shaped_score(sc[nt][2 + e], opt, p1, j, h, Hq);
+                        sc[nt][e] = shaped_score_fast(sc[nt][e], so, p0, j, h, Hq) + far_bias;
+                        sc[nt][2 + e] = shaped_score_fast(sc[nt][2 + e], so, p1, j, h, Hq) + far_bias;
                     }
                 }
             }
@@ -406,10 +426,10 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
                 const int ja = j0 + 2 * tq + e, jb = ja + 8;
                 if (SHAPED) {                                   // rows g and g + 8 are query heads hk G + g and + 8
                     const int ha = min(hk * G + g, Hq - 1), hb = min(hk * G + g + 8, Hq - 1);
-                    s0[e] = zai_shaped_score(s0[e], opt, pos, ja, ha, Hq);
-                    s0[2 + e] = zai_shaped_score(s0[2 + e], opt, pos, ja, hb, Hq);
-                    s1[e] = zai_shaped_score(s1[e], opt, pos, jb, ha, Hq);
-                    s1[2 + e] = zai_shaped_score(s1[2 + e], opt, pos, jb, hb, Hq);
+                    s0[e] = shaped_score_fast(s0[e], opt, pos, ja, ha, Hq);
+                    s0[2 + e] = shaped_score_fast(s0[2 + e], opt, pos, ja, hb, Hq);
+                    s1[e] = shaped_score_fast(s1[e], opt, pos, jb, ha, Hq);
+                    s1[2 + e] = shaped_score_fast(s1[2 + e], opt, pos, jb, hb, Hq);
                 }
                 if (ja < lo || ja >= hi || (SHAPED && ja >= keep && ja < kstart)) { s0[e] = -INFINITY; s0[2 + e] = -INFINITY; }
                 if (jb < lo || jb >= hi || (SHAPED && jb >= keep && jb < kstart)) { s1[e] = -INFINITY; s1[2 + e] = -INFINITY; }

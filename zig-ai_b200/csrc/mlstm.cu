@@ -9,84 +9,103 @@
 // The normaliser n is one more column of S (the column of a value that is always 1), and every column carries its own
 // copy of m in a row behind its D rows: the kept state is [heads, D + 1, Dv + 1], 32-bit, and a column's walk needs
 // nothing from another column.  `mlstm_scan_kernel`: a warp owns 32 columns of one head of one request and walks the
-// request's rows of the step in order, its column of S in registers, the rows' q, k and gates staged in shared memory
-// 16 rows at a time; it leaves S^T q per column, n . q and m per row.  `mlstm_output_kernel` divides, norms and gates.
+// request's rows of the step in order, its column of S in registers, the rows' q, k and gates staged in shared memory a
+// tile of rows at a time by a second warp (the next tile comes in while a tile is walked); it leaves S^T q per column,
+// n . q and m per row.  `mlstm_output_kernel` divides, norms and gates.
 // Gates, decays, the state and the sums are 32-bit in both modes; a row's result depends on the request's rows alone and
 // is the same whether they come as one portion, as several or one by one.
 #include "common.cuh"
 
-#define MLSTM_TT 16          // rows staged at a time
+// Rows staged at a time: as many as make the staged q and k 2 x 1024 values, at most 32 (a lane computes one row's gates).
+template <int DMAX> struct MlstmTile { static constexpr int TT = 1024 / DMAX < 32 ? 1024 / DMAX : 32; };
 
 __device__ __forceinline__ float mlstm_logsigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
+// Two warps a block: warp 1 brings the rows of the next tile from memory into one of two shared buffers (q scaled, k, the
+// lanes' values, the two log gates, all as 32-bit numbers; zeros beyond D and beyond the span) while warp 0, which owns the 32
+// columns, walks the tile before; they meet at one barrier a tile.
 template <typename T, int DMAX>
-__global__ void __launch_bounds__(32) mlstm_scan_kernel(
+__global__ void __launch_bounds__(64) mlstm_scan_kernel(
     float* __restrict__ part, const T* __restrict__ y, int y_stride, int q_at, int k_at, int v_at, int i_at, int f_at,
     const float* __restrict__ bias_i, const float* __restrict__ bias_f, float cap, float* __restrict__ state,
     const int* __restrict__ cu_q, const int* __restrict__ slot_ids, int num_slots, int* __restrict__ status, int H, int D, int Dv,
     int write_state) {
-    extern __shared__ float sm[];
-    float* sq = sm;                               // [TT][D]
-    float* sk = sq + MLSTM_TT * D;                // [TT][D]
-    float* sv = sk + MLSTM_TT * D;                // [TT][32]
-    float* sg = sv + MLSTM_TT * 32;               // [TT][2]  i, f
+    constexpr int TT = MlstmTile<DMAX>::TT, PER = TT * DMAX / 32;      // staged values of q (and of k) a lane brings
+    __shared__ __align__(16) float sq[2][TT * DMAX], sk[2][TT * DMAX], sv[2][TT * 32], sg[2][TT * 2];
     pdl_trigger();
     pdl_wait();
-    const int s = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
+    const int s = blockIdx.x, h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int c = blockIdx.z * 32 + lane;         // this lane's column; column Dv is the normaliser
     const bool live = c <= Dv;
     const int r0 = cu_q[s], r1 = cu_q[s + 1];
     if (r1 <= r0) return;
+    const int n_tiles = (r1 - r0 + TT - 1) / TT;
+
+    if (warp == 1) {                              // ---- the rows' way into shared memory
+        const float qscale = rsqrtf((float)D);
+        const float bi = bias_i[h], bf = bias_f[h];
+        for (int n = 0; n < n_tiles; ++n) {
+            const int t0 = r0 + n * TT, nt = min(TT, r1 - t0), buf = n & 1;
+#pragma unroll 8
+            for (int i = 0; i < PER; ++i) {
+                const int e = lane + 32 * i, tt = e / DMAX, d = e % DMAX;
+                const bool ok = tt < nt && d < D;
+                const T* row = y + (size_t)(t0 + (ok ? tt : 0)) * y_stride + h * D + (ok ? d : 0);
+                sq[buf][e] = ok ? to_float(row[q_at]) * qscale : 0.f;
+                sk[buf][e] = ok ? to_float(row[k_at]) : 0.f;
+            }
+#pragma unroll 8
+            for (int tt = 0; tt < TT; ++tt)
+                sv[buf][tt * 32 + lane] = (tt < nt && c < Dv) ? to_float(y[(size_t)(t0 + tt) * y_stride + v_at + h * Dv + c]) : 1.f;
+            if (lane < nt) {
+                const T* row = y + (size_t)(t0 + lane) * y_stride;
+                sg[buf][2 * lane] = cap * tanhf((to_float(row[i_at + h]) + bi) / cap);
+                sg[buf][2 * lane + 1] = mlstm_logsigmoid(cap * tanhf((to_float(row[f_at + h]) + bf) / cap));
+            }
+            __syncthreads();                      // tile n is there; tile n - 1 has been walked (its buffer is filled next)
+        }
+        __syncthreads();
+        return;
+    }
+
+    // ---- the walk
     const int slot = zai_checked_slot(slot_ids[s], num_slots, status);
     float* st = state + (((size_t)slot * H + h) * (D + 1)) * (Dv + 1);
     float col[DMAX];
 #pragma unroll
     for (int d = 0; d < DMAX; ++d) col[d] = (live && d < D) ? st[(size_t)d * (Dv + 1) + c] : 0.f;
     float m = live ? st[(size_t)D * (Dv + 1) + c] : 0.f;
-    const float qscale = rsqrtf((float)D);
-    const float bi = bias_i[h], bf = bias_f[h];
-    for (int t0 = r0; t0 < r1; t0 += MLSTM_TT) {
-        const int nt = min(MLSTM_TT, r1 - t0);
-        __syncwarp();
-        for (int i = lane; i < nt * D; i += 32) {
-            const int tt = i / D, d = i - tt * D;
-            const T* row = y + (size_t)(t0 + tt) * y_stride;
-            sq[i] = to_float(row[q_at + h * D + d]) * qscale;
-            sk[i] = to_float(row[k_at + h * D + d]);
-        }
-        for (int tt = 0; tt < nt; ++tt)
-            sv[tt * 32 + lane] = c < Dv ? to_float(y[(size_t)(t0 + tt) * y_stride + v_at + h * Dv + c]) : 1.f;
-        if (lane < nt) {
-            const T* row = y + (size_t)(t0 + lane) * y_stride;
-            sg[2 * lane] = cap * tanhf((to_float(row[i_at + h]) + bi) / cap);
-            sg[2 * lane + 1] = mlstm_logsigmoid(cap * tanhf((to_float(row[f_at + h]) + bf) / cap));
-        }
-        __syncwarp();
+    __syncthreads();                              // tile 0 is there
+    for (int n = 0; n < n_tiles; ++n) {
+        const int t0 = r0 + n * TT, nt = min(TT, r1 - t0), buf = n & 1;
         for (int tt = 0; tt < nt; ++tt) {
-            const float gi = sg[2 * tt], gf = sg[2 * tt + 1];
+            const float gi = sg[buf][2 * tt], gf = sg[buf][2 * tt + 1];
             const float m_new = fmaxf(gf + m, gi);
-            const float keep = expf(gf + m - m_new), take = expf(gi - m_new) * sv[tt * 32 + lane];
-            const float* qr = sq + tt * D;
-            const float* kr = sk + tt * D;
-            float a0 = 0.f, a1 = 0.f;
+            const float keep = expf(gf + m - m_new), take = expf(gi - m_new) * sv[buf][tt * 32 + lane];
+            const float* qr = sq[buf] + tt * DMAX;
+            const float* kr = sk[buf] + tt * DMAX;
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+            // (beyond D the staged q and k are zeros and the column stays zero: no bound is checked)
 #pragma unroll
-            for (int d = 0; d < DMAX; d += 2) {
-                if (d < D) {
-                    col[d] = keep * col[d] + take * kr[d];
-                    a0 = fmaf(col[d], qr[d], a0);
-                }
-                if (d + 1 < D) {
-                    col[d + 1] = keep * col[d + 1] + take * kr[d + 1];
-                    a1 = fmaf(col[d + 1], qr[d + 1], a1);
-                }
+            for (int d = 0; d < DMAX; d += 4) {
+                const float4 k4 = *reinterpret_cast<const float4*>(kr + d), q4 = *reinterpret_cast<const float4*>(qr + d);
+                col[d] = fmaf(keep, col[d], take * k4.x);
+                col[d + 1] = fmaf(keep, col[d + 1], take * k4.y);
+                col[d + 2] = fmaf(keep, col[d + 2], take * k4.z);
+                col[d + 3] = fmaf(keep, col[d + 3], take * k4.w);
+                a0 = fmaf(col[d], q4.x, a0);
+                a1 = fmaf(col[d + 1], q4.y, a1);
+                a2 = fmaf(col[d + 2], q4.z, a2);
+                a3 = fmaf(col[d + 3], q4.w, a3);
             }
             m = m_new;
             if (live) {
                 float* o = part + ((size_t)(t0 + tt) * H + h) * (Dv + 2);
-                o[c] = a0 + a1;
+                o[c] = (a0 + a1) + (a2 + a3);
                 if (c == Dv) o[Dv + 1] = m_new;
             }
         }
+        __syncthreads();                          // this tile's buffer may be filled again; the next tile is there
     }
     if (write_state && live) {
 #pragma unroll
@@ -129,9 +148,8 @@ ZAI_API int zai_mlstm(void* out, float* part, const void* y, int y_stride, int d
     if (N <= 0 || S <= 0) return ZAI_OK;
     if (H < 1 || H > 65535 || D < 1 || D > 256 || Dv < 1 || cap <= 0.f) return ZAI_BAD_SIZE;
     const dim3 grid(S, H, (Dv + 1 + 31) / 32);
-    const size_t smem = ((size_t)2 * MLSTM_TT * D + MLSTM_TT * 32 + 2 * MLSTM_TT) * sizeof(float);
     int rc;
-#define MLSTM_GO(DM) ZAI_DISPATCH(dtype, rc = launch_pdl(mlstm_scan_kernel<T, DM>, grid, dim3(32), smem, stream, part, (const T*)y, \
+#define MLSTM_GO(DM) ZAI_DISPATCH(dtype, rc = launch_pdl(mlstm_scan_kernel<T, DM>, grid, dim3(64), 0, stream, part, (const T*)y, \
         y_stride, q_at, k_at, v_at, i_at, f_at, bias_i, bias_f, cap, state, cu_q, slot_ids, num_slots, status, H, D, Dv, write_state))
     if (D <= 16) MLSTM_GO(16);
     else if (D <= 32) MLSTM_GO(32);
