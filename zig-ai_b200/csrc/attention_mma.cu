@@ -117,15 +117,14 @@ __device__ __forceinline__ void pv_16keys(float (&o)[D / 8][4], const uint32_t (
     }
 }
 
-// `zai_shaped_score` for these kernels: the cap's tanh as 1 - 2 / (1 + e^(2x)) with the approximate exponential and division
+// `zai_shaped_score` (common.cuh) for these kernels: the cap's tanh as 1 - 2 / (1 + e^(2x)) with the approximate exponential and division
 // (an absolute error of a few 1e-6 of the cap, far below what the bfloat16 rounding of q and k leaves in a score).
-__device__ __forceinline__ float shaped_score_fast(float dot, const ZaiScoreOptions& opt, int pos, int j, int h, int Hq) {
-    float s = dot * opt.scale;
-    if (opt.softcap > 0.f) {
-        const float e = fast_exp2(s * __fdividef(2.8853900817779268f, opt.softcap));
-        s = opt.softcap * (1.f - __fdividef(2.f, 1.f + e));
-    }
-    if (opt.bias) s += __ldg(opt.bias + (size_t)min(max(pos - j, 0), opt.bias_rows - 1) * Hq + h);
+// `cap2` = 2 log2(e) / cap (0: no cap); `bias_h`: the table's column of this head (or null), `last` its last row.
+__device__ __forceinline__ float shaped_score_fast(float dot, float scale, float cap, float cap2, const float* __restrict__ bias_h,
+                                                   int last, int Hq, int dist) {
+    float s = dot * scale;
+    if (cap2 > 0.f) s = cap * (1.f - __fdividef(2.f, 1.f + fast_exp2(s * cap2)));
+    if (bias_h) s += __ldg(bias_h + (size_t)min(max(dist, 0), last) * Hq);
     return s;
 }
 
@@ -136,7 +135,7 @@ __device__ __forceinline__ float shaped_score_fast(float dot, const ZaiScoreOpti
 // SHAPED: the scores pass `zai_shaped_score` (scale_log2 is then log2(e) alone), the sink joins the sums at the end, and
 // under a window the tiles of the kept first positions are walked before the window's.
 template <int D, bool SHAPED>
-__global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_mma_kernel(
+__global__ void __launch_bounds__(PREFILL_WARPS * 32, (D <= 64 ? 2 : 1)) prefill_mma_kernel(
     bf16* __restrict__ out, const bf16* __restrict__ q, const bf16* __restrict__ pages,
     const int* __restrict__ block_table, int table_width, const int* __restrict__ cu_q,
     const int* __restrict__ ctx_lens, int S, int page_size, int Hq, int Hkv, float scale_log2, int window,
@@ -239,19 +238,21 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_mma_kernel(
             if (SHAPED) {
                 // a tile that lies beyond the bias table's last row for all of the warp's rows gets that row's value
                 // without a lookup (the table ends at the first distance of its last bucket: most tiles of a long context)
-                ZaiScoreOptions so = opt;
+                const float cap2 = opt.softcap > 0.f ? __fdividef(2.8853900817779268f, opt.softcap) : 0.f;
+                const int last = opt.bias_rows - 1;
+                const float* bias_h = opt.bias ? opt.bias + h : nullptr;
                 float far_bias = 0.f;
-                if (opt.bias && (ctx + i0 + warp * 16) - (t * TILE + TILE - 1) >= opt.bias_rows - 1) {
-                    far_bias = __ldg(opt.bias + (size_t)(opt.bias_rows - 1) * Hq + h);
-                    so.bias = nullptr;
+                if (bias_h && (ctx + i0 + warp * 16) - (t * TILE + TILE - 1) >= last) {
+                    far_bias = __ldg(bias_h + (size_t)last * Hq);
+                    bias_h = nullptr;
                 }
 #pragma unroll
                 for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const int j = t * TILE + nt * 8 + 2 * tq + e;
-                        sc[nt][e] = shaped_score_fast(sc[nt][e], so, p0, j, h, Hq) + far_bias;
-                        sc[nt][2 + e] = shaped_score_fast(sc[nt][2 + e], so, p1, j, h, Hq) + far_bias;
+                        sc[nt][e] = shaped_score_fast(sc[nt][e], opt.scale, opt.softcap, cap2, bias_h, last, Hq, p0 - j) + far_bias;
+                        sc[nt][2 + e] = shaped_score_fast(sc[nt][2 + e], opt.scale, opt.softcap, cap2, bias_h, last, Hq, p1 - j) + far_bias;
                     }
                 }
             }
@@ -425,11 +426,14 @@ __global__ void __launch_bounds__(NTHREADS) decode_mma_kernel(
             for (int e = 0; e < 2; ++e) {
                 const int ja = j0 + 2 * tq + e, jb = ja + 8;
                 if (SHAPED) {                                   // rows g and g + 8 are query heads hk G + g and + 8
-                    const int ha = min(hk * G + g, Hq - 1), hb = min(hk * G + g + 8, Hq - 1);
-                    s0[e] = shaped_score_fast(s0[e], opt, pos, ja, ha, Hq);
-                    s0[2 + e] = shaped_score_fast(s0[2 + e], opt, pos, ja, hb, Hq);
-                    s1[e] = shaped_score_fast(s1[e], opt, pos, jb, ha, Hq);
-                    s1[2 + e] = shaped_score_fast(s1[2 + e], opt, pos, jb, hb, Hq);
+                    const float cap2 = opt.softcap > 0.f ? __fdividef(2.8853900817779268f, opt.softcap) : 0.f;
+                    const float* ba = opt.bias ? opt.bias + min(hk * G + g, Hq - 1) : nullptr;
+                    const float* bb = opt.bias ? opt.bias + min(hk * G + g + 8, Hq - 1) : nullptr;
+                    const int last = opt.bias_rows - 1;
+                    s0[e] = shaped_score_fast(s0[e], opt.scale, opt.softcap, cap2, ba, last, Hq, pos - ja);
+                    s0[2 + e] = shaped_score_fast(s0[2 + e], opt.scale, opt.softcap, cap2, bb, last, Hq, pos - ja);
+                    s1[e] = shaped_score_fast(s1[e], opt.scale, opt.softcap, cap2, ba, last, Hq, pos - jb);
+                    s1[2 + e] = shaped_score_fast(s1[2 + e], opt.scale, opt.softcap, cap2, bb, last, Hq, pos - jb);
                 }
                 if (ja < lo || ja >= hi || (SHAPED && ja >= keep && ja < kstart)) { s0[e] = -INFINITY; s0[2 + e] = -INFINITY; }
                 if (jb < lo || jb >= hi || (SHAPED && jb >= keep && jb < kstart)) { s1[e] = -INFINITY; s1[2 + e] = -INFINITY; }
