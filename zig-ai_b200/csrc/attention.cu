@@ -13,12 +13,9 @@
 // so a row's result does not depend on how the request was cut into steps or on its batch.
 // Pages: [num_pages, 2, Hkv, page_size, D].
 //
-// Options of designs that shape their scores (`ZaiScoreOptions`, all off by default):
-//   softcap     s <- cap * tanh(s / cap), before anything is added
-//   bias        s <- s + bias[min(pos - j, bias_rows - 1), head]: a table by distance (made on the host from the
-//               design's buckets), added after the cap and not scaled
-//   sink        one more term exp(sink[head]) in the softmax's denominator, with no key and no value
-//   keep_first  with a window: the first keep_first positions of the request stay visible (at their true positions)
+// `zai_paged_attention_scored` is the same kernel with the options of designs that shape their scores (`ZaiScoreOptions`
+// in common.cuh: a cap, a bias by distance, a sink, kept first positions under a window; here with the exact `tanhf`).
+// The kept positions are a second range of keys, walked before the window's, again in steps of 32 from position 0.
 #include "common.cuh"
 
 

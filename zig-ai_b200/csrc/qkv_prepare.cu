@@ -6,6 +6,8 @@
 //                       pairs (x[i], x[i + rot/2]), i < rot/2, of every head turn by the row's (cos, sin) table
 //                       q -> [N, Hq, Dp],  k, v -> pages[page(pos), 0|1, kv head, pos % page_size, :Dp]
 //                       (Dp >= D, Dv: zeros behind a head's own values; zeros change neither a score nor a sum)
+//                       optionally the queries times 1 + coef * ln(floor((pos + 1) / every) + 1), and the cached values
+//                       (1 - lambda) v + lambda v_first with an earlier layer's values of the same rows
 //   zai_latent_prepare  the rotated parts of the queries of latent attention, and per row the normed latent and the
 //                       rotated shared key part into pages[page(pos), pos % page_size, :rank + rot]
 //   zai_sigmoid_gate    out = o * sigmoid(gate), the gate one number per head or per element
