@@ -872,10 +872,10 @@ def lolivik_config(width, layers=16, vocab=65536):
     att = {"heads": heads, "kv_heads": heads // 4, "dim": 64, "vdim": 64, "scale": 0.125, "softcap": 30.0, "bias_rows": 32,
            "bias_max": 4096, "q_temp": {"coef": 0.1, "every": 1024}, "v_mix": True}
     win = {"heads": heads, "kv_heads": heads // 4, "dim": 64, "vdim": 64, "scale": 0.125, "mask": {"size": 1024, "keep_first": 4},
-           "rot": {"base": 1e6, "dims": 32, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}, "v_mix": True}
-    mem = {"heads": heads // 2, "dim": 64, "vdim": 128, "gate_cap": 15.0}
+           "rot": {"base": 5e5, "dims": 32, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 8192}}, "v_mix": True}
+    mem = {"heads": heads // 2, "dim": 64, "vdim": 128, "gate_cap": 12.0}
     group = [("attention", att, dense), ("mlstm", mem, moe), ("attention_2", win, moe), ("mlstm", mem, dense)]
-    return {"architecture": "Lolivik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.3,
+    return {"architecture": "Lolivik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
             "layers": [{"type": t, "mixer": dict(m), "mlp": dict(f)} for t, m, f in (group[i % 4] for i in range(layers))]}
 
 

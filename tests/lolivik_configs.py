@@ -51,7 +51,7 @@ L_B = config(257, 66, 1e-6, 1.0, [
     memory(2, 16, 8, 20.0, mlp=moe(32, 2.0, 3, 1, shared=(16, 1.0))),
     attention(3, 3, 16, 20, 0.2, 8.0, 16, 100, 0.3, 32, mlp=dense(100)),
     windowed(6, 3, 16, 20, 0.25, 40, 0, 500.0, 16, None, mlp=moe(40, 2.0, 7, 3)),
-    windowed(6, 3, 8, 20, 0.35, 5, 9, 300.0, 4, stretch(8.0, 1.0, 4.0, 64)),
+    windowed(6, 3, 8, 20, 0.35, 5, 9, 300.0, 4, stretch(8.0, 2.0, 5.0, 64)),
     attention(3, 1, 24, 60, 0.15, 50.0, 4, 9, 0.0, 1, v_mix=False, mlp=moe(16, 4.0, 2, 2, shared=(40, 2.0))),
 ])
 
@@ -61,7 +61,7 @@ ONLY = {
     "attention_dense": config(97, 40, 1e-5, 1.0, [attention(2, 2, 12, 12, 0.25, 20.0, 8, 30, 0.5, 4, v_mix=False, mlp=dense(64))]),
     "windowed": config(97, 40, 1e-5, 0.7, [windowed(4, 1, 12, 8, 0.3, 9, 2, 10000.0, 6, stretch(4.0, 1.0, 2.0, 32))]),
     "windowed_plain": config(97, 40, 1e-5, 0.3, [windowed(3, 3, 8, 16, 0.35, 20, 0, 100.0, 8, None, v_mix=False)]),
-    "memory": config(97, 40, 1e-5, 0.7, [memory(3, 10, 14, 15.0)]),
+    "memory": config(97, 40, 1e-5, 0.7, [memory(3, 10, 14, 14.0)]),
     "memory_experts": config(97, 40, 1e-5, 1.0, [memory(2, 6, 10, 8.0, mlp=moe(24, 2.0, 6, 2, shared=(12, 2.0)))]),
     "experts_one_of_many": config(97, 40, 1e-5, 1.0, [memory(2, 8, 8, 12.0, mlp=moe(12, 1.0, 9, 1))]),
     "mixed_values": config(97, 40, 1e-5, 0.6, [windowed(2, 2, 8, 10, 0.3, 12, 1, 1000.0, 8, None),
@@ -75,8 +75,8 @@ ONLY = {
 # sizes that the tensor-core kernels and the few-rows product kernels take, for the whole-model GPU tests in bfloat16
 L_C = config(1000, 320, 1e-6, 0.4, [
     attention(8, 2, 64, 64, 0.125, 25.0, 32, 1000, 0.25, 64, mlp=dense(512)),
-    memory(4, 64, 64, 15.0, mlp=moe(128, 2.0, 8, 2, shared=(192, 2.0))),
-    windowed(4, 4, 64, 32, 0.125, 100, 4, 10000.0, 32, stretch(8.0, 1.0, 4.0, 256), mlp=moe(64, 3.0, 4, 1)),
+    memory(4, 64, 64, 13.0, mlp=moe(128, 2.5, 8, 2, shared=(192, 2.0))),
+    windowed(4, 4, 64, 32, 0.125, 100, 4, 10000.0, 32, stretch(6.0, 1.0, 3.0, 256), mlp=moe(64, 3.0, 4, 1)),
     memory(2, 32, 128, 12.0, mlp=dense(448)),
     attention(4, 2, 32, 64, 0.18, 30.0, 16, 300, 0.3, 128, mlp=moe(96, 2.0, 6, 3, shared=(64, 1.5))),
 ])
