@@ -46,21 +46,35 @@ __global__ void __launch_bounds__(64) mlstm_scan_kernel(
         const float bi = bias_i[h], bf = bias_f[h];
         for (int n = 0; n < n_tiles; ++n) {
             const int t0 = r0 + n * TT, nt = min(TT, r1 - t0), buf = n & 1;
-#pragma unroll 8
+            // all of the tile's loads are issued before any of them is used: one trip to memory a tile, not one a batch
+            T fq[PER], fk[PER], fv[TT];
+            float gate_i = 0.f, gate_f = 0.f;
+#pragma unroll
             for (int i = 0; i < PER; ++i) {
                 const int e = lane + 32 * i, tt = e / DMAX, d = e % DMAX;
                 const bool ok = tt < nt && d < D;
                 const T* row = y + (size_t)(t0 + (ok ? tt : 0)) * y_stride + h * D + (ok ? d : 0);
-                sq[buf][e] = ok ? to_float(row[q_at]) * qscale : 0.f;
-                sk[buf][e] = ok ? to_float(row[k_at]) : 0.f;
+                fq[i] = ok ? row[q_at] : from_float<T>(0.f);
+                fk[i] = ok ? row[k_at] : from_float<T>(0.f);
             }
-#pragma unroll 8
+#pragma unroll
             for (int tt = 0; tt < TT; ++tt)
-                sv[buf][tt * 32 + lane] = (tt < nt && c < Dv) ? to_float(y[(size_t)(t0 + tt) * y_stride + v_at + h * Dv + c]) : 1.f;
+                fv[tt] = (tt < nt && c < Dv) ? y[(size_t)(t0 + tt) * y_stride + v_at + h * Dv + c] : from_float<T>(1.f);
             if (lane < nt) {
                 const T* row = y + (size_t)(t0 + lane) * y_stride;
-                sg[buf][2 * lane] = cap * tanhf((to_float(row[i_at + h]) + bi) / cap);
-                sg[buf][2 * lane + 1] = mlstm_logsigmoid(cap * tanhf((to_float(row[f_at + h]) + bf) / cap));
+                gate_i = to_float(row[i_at + h]);
+                gate_f = to_float(row[f_at + h]);
+            }
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                sq[buf][lane + 32 * i] = to_float(fq[i]) * qscale;
+                sk[buf][lane + 32 * i] = to_float(fk[i]);
+            }
+#pragma unroll
+            for (int tt = 0; tt < TT; ++tt) sv[buf][tt * 32 + lane] = to_float(fv[tt]);
+            if (lane < nt) {
+                sg[buf][2 * lane] = cap * tanhf((gate_i + bi) / cap);
+                sg[buf][2 * lane + 1] = mlstm_logsigmoid(cap * tanhf((gate_f + bf) / cap));
             }
             __syncthreads();                      // tile n is there; tile n - 1 has been walked (its buffer is filled next)
         }
