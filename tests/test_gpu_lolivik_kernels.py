@@ -94,7 +94,9 @@ def test_attention_with_shaped_scores(dtype, Hq, Hkv, D, ps):
     o = ops()
     g = torch.Generator().manual_seed(8)
     bias, sink = distance_bias(37, Hq, g), (torch.randn(Hq, generator=g) * 2).cuda()
-    for ctx, q_lens in (([0, ps - 1, 2 * ps, 301, 5, 63], [150, 2, 1, 1, 37, 66]), ([0, 1, 254, 255, 256, 700, 63, 1029], [1] * 8)):
+    # (the third step: nine decoding requests in front of two portions, of which eight go to the kernel for single tokens)
+    for ctx, q_lens in (([0, ps - 1, 2 * ps, 301, 5, 63], [150, 2, 1, 1, 37, 66]), ([0, 1, 254, 255, 256, 700, 63, 1029], [1] * 8),
+                        ([3, 70, 0, 129, 64, 300, 31, 32, 5, 0, 200], [1] * 9 + [70, 131])):
         num_pages = sum(-(-(c + n) // ps) for c, n in zip(ctx, q_lens)) + 8
         step = make_step(o, dtype, ctx, q_lens, ps, num_pages, 9)
         pages = fill_pages(step, ctx, q_lens, ps, Hkv, D, dtype, num_pages, g)

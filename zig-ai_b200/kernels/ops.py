@@ -909,22 +909,30 @@ def paged_attention(q, step, cache, heads, kv_heads, head_dim, scale, window=Non
         if (impl != "general" and q.dtype == torch.bfloat16 and q.is_contiguous()
                 and _fn("attention_mma", "zai_attention_mma_supports")(head_dim, heads, kv_heads)):
             # the tensor-core kernels with the scores shaped inside them
-            if step.decode_only:
+            def single_tokens(n):
+                # rows 0..n-1 are one token each, row i of span i: keys split over blocks, then combined (with the sink)
                 keys = _fn("attention_mma", "zai_decode_chunk_keys")()
                 n_chunks = max(-(-int(step.max_kv_len) // keys), 1)
-                part_o = torch.empty((N, heads, n_chunks, head_dim), dtype=torch.float32, device=q.device)
-                part_ml = torch.empty((N, heads, n_chunks, 2), dtype=torch.float32, device=q.device)
+                part_o = torch.empty((n, heads, n_chunks, head_dim), dtype=torch.float32, device=q.device)
+                part_ml = torch.empty((n, heads, n_chunks, 2), dtype=torch.float32, device=q.device)
                 _check(_fn("attention_mma", "zai_decode_attention_mma_scored")(
-                    _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(q), _ptr(cache.pages), _ptr(bt), bt.shape[1], _ptr(step.positions), N,
+                    _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(q), _ptr(cache.pages), _ptr(bt), bt.shape[1], _ptr(step.positions), n,
                     n_chunks, cache.page_size, heads, kv_heads, head_dim, float(scale), int(window or 0), cache.pages.shape[0],
                     _status_ptr(q.device), *shaped, _stream()), "decode attention (scored)", 2)
+
+            if step.decode_only:
+                single_tokens(N)
                 return out
+            # the one-token spans at the front of a mixed step go to the kernel for single tokens, as without shaping
+            ns = int(getattr(step, "single_first", 0)) if SPLIT_MIXED_ATTENTION else 0
+            if ns:
+                single_tokens(ns)
             block_rows = _fn("attention_mma", "zai_prefill_block_rows")()
-            n_tiles = step.attn_tiles if getattr(step, "attn_tiles", None) else sum(-(-n // block_rows) for n in step.q_lens)
+            n_tiles = (step.attn_tiles - ns) if getattr(step, "attn_tiles", None) else sum(-(-n // block_rows) for n in step.q_lens[ns:])
             _check(_fn("attention_mma", "zai_prefill_attention_mma_scored")(
-                _ptr(out), _ptr(q), _ptr(cache.pages), _ptr(bt), bt.shape[1], _ptr(step.cu_q), _ptr(step.ctx_lens), step.n_seqs,
-                n_tiles, cache.page_size, heads, kv_heads, head_dim, float(scale), int(window or 0), cache.pages.shape[0],
-                _status_ptr(q.device), *shaped, _stream()), "prefill attention (scored)")
+                _ptr(out), _ptr(q), _ptr(cache.pages), _ptr(bt[ns:]), bt.shape[1], _ptr(step.cu_q[ns:]), _ptr(step.ctx_lens[ns:]),
+                step.n_seqs - ns, n_tiles, cache.page_size, heads, kv_heads, head_dim, float(scale), int(window or 0),
+                cache.pages.shape[0], _status_ptr(q.device), *shaped, _stream()), "prefill attention (scored)")
             return out
         _check(_fn("attention", "zai_paged_attention_scored")(
             _ptr(out), _ptr(q), _ptr(cache.pages), _dt(q), _ptr(bt), bt.shape[1], _ptr(step.positions), _ptr(step.seq_idx),
